@@ -111,7 +111,16 @@ class CacheManager:
         self.groups: list[CacheGroup] = []
         self.layer_group: dict[int, int] = {}
         self.state_layers: dict[int, FixedStateNeed] = {}
+        # a layer may keep several things (a mixer of two sides: pages for one, a state row for the other): its need is
+        # then a tuple, every member is kept under the key (layer, member), and the layer's view is a tuple of views
+        self.composite = {layer: len(need) for layer, need in enumerate(needs) if isinstance(need, (tuple, list))}
+        flat = []
         for layer, need in enumerate(needs):
+            if isinstance(need, (tuple, list)):
+                flat += [((layer, j), sub) for j, sub in enumerate(need)]
+            else:
+                flat.append((layer, need))
+        for layer, need in flat:
             if need is None:
                 continue
             if isinstance(need, FixedStateNeed):
@@ -146,6 +155,8 @@ class CacheManager:
                 views[layer] = PagedLayerCache(group=g, k=grp.k[i], v=grp.v[i])
         for layer, need in self.state_layers.items():
             views[layer] = StateLayerCache(self.slots.add_layer(layer, need.shape, need.dtype, device))
+        for layer, members in self.composite.items():
+            views[layer] = tuple(views.pop((layer, j), None) for j in range(members))
         return views
 
     def bytes_per_page(self, itemsize: int) -> int:

@@ -20,7 +20,7 @@ class NormSpec:
     size: int
     eps: float
     name: str                      # tensor name of the weight, relative to the owner's prefix
-    kind: str = "rmsnorm"
+    kind: str = "rmsnorm"          # "rmsnorm", or "dyt": tanh(alpha * x) * weight + bias (`<name>.alpha`, `<name>.b`)
 
 
 @dataclass(frozen=True)
@@ -86,10 +86,63 @@ class GeneralAttentionSpec:
     score_bias: bool = False                # a number per head added to the score (sigmoid weights)
     twin: Optional[TwinMapsSpec] = None
     gate: Optional[str] = None              # "head": one sigmoid gate a head; "element": one per output element
+    head_temperature: bool = False          # a learned number per query head multiplies its scaled scores
+    # a learned bias by distance, added to the score after scale and temperature: (buckets or None = the table's own
+    # row count, the distance from which the last bucket serves); see parts.general_attention.distance_buckets
+    distance_bias: Optional[tuple] = None
+    sink: bool = False                      # exp(a learned number per head) counts once in the softmax's denominator
     prefix: str = "mix"
-    # tensor names below the prefix: queries, keys, values, gate, output, whole-projection norms, score bias
-    names: tuple = ("q", "k", "v", "g", "o", "q.norm", "k.norm", "pb")
+    # tensor names below the prefix: queries, keys, values, gate, output, whole-projection norms, score bias,
+    # temperature, distance bias, sink
+    names: tuple = ("q", "k", "v", "g", "o", "q.norm", "k.norm", "pb", "temp", "rel", "sink")
     kind: str = "general_attention"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """A matrix state per head under the generalized delta rule (per token: a decay per key channel, the removal of
+    what the state holds along the unit key, then the new key-value pair); keys and values of one size.  The decay
+    comes from a low-rank pair of matrices whose rank is the first matrix's row count."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    norm_eps: float                # of the per-head unit norm of the output
+    decay_rank: Optional[int] = None   # None: taken from the tensor
+    prefix: str = "mix"
+    # receptance, key, value, output gate, removal gate and its bias, decay down- and up-projection and its bias,
+    # output norm weight, output projection
+    names: tuple = ("r", "k", "v", "g", "a", "a.b", "w1", "w2", "w0", "norm", "o")
+    kind: str = "delta_rule"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """A matrix memory per head with an exponential input gate, a sigmoid forget gate (both capped by tanh in the log
+    domain), a normaliser vector and a running maximum that keeps the exponentials in range."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    norm_eps: float
+    prefix: str = "mix"
+    # query, key, value, output gate, input gate and its bias, forget gate and its bias, output norm weight, output
+    names: tuple = ("q", "k", "v", "g", "i", "i.b", "f", "f.b", "norm", "o")
+    kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class MixerPairSpec:
+    """Two mixers that read the same input; the result is coef * (rms(left) * w_left + rms(right) * w_right) with a
+    plain RMSNorm over the model width on each output."""
+    hidden_size: int
+    left: Any
+    right: Any
+    eps: float
+    coef: float = 0.5
+    prefix: str = "mix"
+    names: tuple = ("left.out", "right.out")
+    kind: str = "mixer_pair"
 
 
 @dataclass(frozen=True)
@@ -97,7 +150,7 @@ class DenseMLPSpec:
     """A feed-forward without a gate: down(act(up(x)))."""
     hidden_size: int
     intermediate_size: int
-    activation: str = "relu2"               # relu(z)^2
+    activation: str = "relu2"               # "relu2": relu(z)^2; "gelu": the exact (erf) gelu; "tanh"
     prefix: str = "mlp"
     names: tuple = ("up", "down")
     kind: str = "dense_mlp"
@@ -136,9 +189,14 @@ class RoutedExpertsSpec:
     expert_size: int
     n_groups: int = 1
     keep_groups: int = 1
-    scoring: str = "softmax"       # router scores: softmax over all experts
+    scoring: str = "softmax"       # router scores: "softmax" over all experts, or "sigmoid" of each logit
     renormalize: bool = False      # whether the chosen scores are made to sum to one
-    activation: str = "gelu"       # exact (erf) gelu
+    activation: str = "gelu"       # "gelu": down(gelu(up x)), exact (erf) gelu; "clamped_glu": experts with a gate
+                                   #   matrix, g = min(gate x, limit), u = clamp(up x, +-limit), down(g sigmoid(1.702 g) (u + 1))
+    group_score: str = "max"       # a group's score: its best expert's ("max") or the sum of its two best ("top2_sum")
+    renorm_eps: float = 0.0        # added to the chosen scores' sum before the division
+    weight_scale: float = 1.0      # multiplies the weights at the end
+    limit: float = 0.0             # of the clamped activation
     prefix: str = "mlp"
     kind: str = "routed_experts"
 
@@ -168,6 +226,9 @@ class LayerSpec:
     cache_from: Optional[int] = None
     kind: str = "pre_norm"
     residual_scale: float = 1.0    # multiplies every branch before it is added to the stream
+    # pre_norm: tensor names (below the prefix) of a gate on each sublayer's result, sigmoid(W x + b) element by
+    # element with x the sublayer's input (`<name>` [hidden, hidden], `<name>.b`), or None
+    residual_gates: Optional[tuple] = None
     token_input: Any = None        # a further branch fed by the token id (TokenInputSpec), or None
 
 
@@ -185,6 +246,12 @@ class ModelSpec:
     # places in the run order (indices into `run_order()`) right before which the embedding output is added to the
     # stream once more
     reinject: tuple = field(default=())
+    # a learned vector per position added to the embedding: tensor [max_position, hidden], or None
+    position_table_name: Optional[str] = None
+    # learned vectors added to every token's stream right before places of the run order: (tensor name [rows, hidden],
+    # ((place, row), ...)), or None
+    pass_vectors: Optional[tuple] = None
+    logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap)
 
     def run_order(self) -> tuple:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))

@@ -128,7 +128,15 @@ JV_EXPORT int jv_swiglu(const void* gu, void* act, int dtype, int n, int inter, 
 }
 
 // Ungated activations of a plain feed-forward down(act(up(x))), on a column range of a wider row and into
-// a column range of a wider row (in and out may be parts of packed tensors): kind 0 = relu(z)^2.
+// a column range of a wider row (in and out may be parts of packed tensors): kind 0 = relu(z)^2, 1 = the exact
+// gelu z/2 (1 + erf(z / sqrt 2)), 2 = tanh.
+__device__ __forceinline__ float unary_act(int kind, float z) {
+  if (kind == 1) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+  if (kind == 2) return tanhf(z);
+  const float r = fmaxf(z, 0.f);
+  return r * r;
+}
+
 template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, long long out_stride,
                                  int cols, size_t total, int kind) {
@@ -139,9 +147,7 @@ __global__ void unary_act_kernel(const T* __restrict__ in, long long in_stride, 
   for (; idx < total; idx += stride) {
     const size_t n = idx / cols;
     const int i = (int)(idx - n * cols);
-    const float z = to_f32(in[n * in_stride + i]);
-    const float r = fmaxf(z, 0.f);
-    out[n * out_stride + i] = from_f32<T>(r * r);
+    out[n * out_stride + i] = from_f32<T>(unary_act(kind, to_f32(in[n * in_stride + i])));
   }
 }
 
@@ -163,10 +169,7 @@ __global__ void unary_act_vec_kernel(const T* __restrict__ in, long long in_stri
     uint4 o4;
     T* o = reinterpret_cast<T*>(&o4);
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const float r = fmaxf(to_f32(z[k]), 0.f);
-      o[k] = from_f32<T>(r * r);
-    }
+    for (int k = 0; k < V; ++k) o[k] = from_f32<T>(unary_act(kind, to_f32(z[k])));
     *reinterpret_cast<uint4*>(out + n * out_stride + i) = o4;
   }
 }
@@ -175,7 +178,7 @@ JV_EXPORT int jv_unary_act(const void* in, long long in_stride, void* out, long 
                            int kind, cudaStream_t stream) {
   const size_t total = (size_t)n * cols;
   if (total == 0) return JV_OK;
-  if (kind != 0) return JV_ERR_UNSUPPORTED;
+  if (kind < 0 || kind > 2) return JV_ERR_UNSUPPORTED;
   const int vec = dtype == 0 ? 4 : 8;
   if (cols % vec == 0 && in_stride % vec == 0 && out_stride % vec == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0) {
     const size_t total_vec = total / vec;
@@ -190,4 +193,50 @@ JV_EXPORT int jv_unary_act(const void* in, long long in_stride, void* out, long 
   JV_DISPATCH_DTYPE(dtype, T, return jv_launch(unary_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
                                                 (const T*)in, in_stride, (T*)out, out_stride, cols, total, kind));
   return JV_ERR_UNSUPPORTED;
+}
+
+// Gated activation with clamps: gu holds [gate | up] (inter columns each) per row;
+//   g = min(gate, limit), u = clamp(up, -limit, limit), act = g * sigmoid(slope * g) * (u + 1), in 32-bit.
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total, float limit,
+                                   float slope) {
+  pdl_trigger();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const size_t n = idx / inter;
+    const int i = (int)(idx - n * inter);
+    const float g = fminf(to_f32(gu[n * 2 * inter + i]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[n * 2 * inter + inter + i]), -limit), limit);
+    act[idx] = from_f32<T>(g / (1.f + expf(-slope * g)) * (u + 1.f));
+  }
+}
+
+JV_EXPORT int jv_glu_clamped(const void* gu, void* act, int dtype, int n, int inter, float limit, float slope,
+                             cudaStream_t stream) {
+  const size_t total = (size_t)n * inter;
+  if (total == 0) return JV_OK;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  JV_DISPATCH_DTYPE(dtype, T, return jv_launch(glu_clamped_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu,
+                                               (T*)act, inter, total, limit, slope));
+  return JV_ERR_UNSUPPORTED;
+}
+
+// x <- cap * tanh(x / cap) in place, on 32-bit values (logits).
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) x[idx] = cap * tanhf(x[idx] / cap);
+}
+
+JV_EXPORT int jv_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return JV_OK;
+  if (!(cap > 0.f)) return JV_ERR_UNSUPPORTED;
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  return jv_launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, x, (size_t)total, cap);
 }

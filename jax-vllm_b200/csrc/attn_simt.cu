@@ -39,6 +39,10 @@ struct AttnParams {
   int sigmoid;               // 1: the weight of a visible key is sigmoid(score + bias[query head]), not normalised over keys
   const float* bias;         // [n_q_heads] or null
   int out_f32;               // 1: `out` is float whatever the type of q and the cache
+  const float* head_scale;   // [n_q_heads] or null: multiplies the scaled score of its head (a temperature per head)
+  const float* dist_bias;    // [n_dist][n_q_heads] or null: added to the score of a key `pos - j` positions back; distances
+  int n_dist;                //   of n_dist - 1 and more share the last row.  Neither `scale` nor `head_scale` touch it.
+  const float* sink;         // [n_q_heads] or null (softmax): exp(sink) counts once in the denominator, with no value
   int* status;
 };
 
@@ -144,6 +148,11 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
         const int pos = row_pos[m];
         const bool vis = pos >= 0 && j < j_hi && j <= pos && (p.window <= 0 || j > pos - p.window);
         float sc = s[r] * p.scale;
+        if (p.head_scale != nullptr || p.dist_bias != nullptr) {
+          const int hq = min(hg * p.heads_per_tile + m % p.heads_per_tile, G - 1) + kv_head * G;
+          if (p.head_scale != nullptr) sc *= p.head_scale[hq];
+          if (p.dist_bias != nullptr && vis) sc += p.dist_bias[(size_t)min(pos - j, p.n_dist - 1) * p.n_q_heads + hq];
+        }
         if (p.score_cap > 0.f) sc = p.score_cap * tanhf(sc / p.score_cap);
         if (p.sigmoid) {
           // ---- weights that do not depend on one another: no maximum, no sum
@@ -210,7 +219,12 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
           p.part_ml[slot * 2 + 1] = row_l[m];
         }
       } else {
-        const float o = acc[m][c] / row_l[m];
+        float o = acc[m][c] / row_l[m];
+        if (p.sink != nullptr) {          // the sink joins the denominator: rescaled to the larger of the two maxima
+          const float sk = p.sink[head], mx = fmaxf(row_m[m], sk);
+          const float e = expf(row_m[m] - mx);
+          o = acc[m][c] * e / (row_l[m] * e + expf(sk - mx));
+        }
         if (p.out_f32) ((float*)p.out)[token * p.out_stride + (size_t)head * DV + d] = o;
         else ((T*)p.out)[token * p.out_stride + (size_t)head * DV + d] = from_f32<T>(o);
       }
@@ -244,9 +258,9 @@ __global__ void attn_combine_kernel(const AttnParams p) {
     }
     return;
   }
-  float m_all = -INFINITY;
+  float m_all = p.sink != nullptr ? p.sink[head] : -INFINITY;
   for (int s = s_first; s <= s_last; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
-  float l_all = 0.f;
+  float l_all = p.sink != nullptr ? expf(p.sink[head] - m_all) : 0.f;
   for (int s = s_first; s <= s_last; ++s)
     l_all += expf(p.part_ml[(base + s) * 2] - m_all) * p.part_ml[(base + s) * 2 + 1];
   const size_t token = (size_t)p.cu_seqlens[entry];
@@ -279,6 +293,7 @@ JV_EXPORT int jv_attn_simt_tokens_per_tile(int n_q_heads, int n_kv_heads) {
 // v_dim: how many leading elements of a value row are used (0: all head_dim); out and part_o then have v_dim
 // elements per head.  A cache whose values are the leading part of its keys passes the same tensor twice.
 // jv_attn_simt_ex: keys and values of different sizes and head counts, capped scores, sigmoid weights, float output
+// a temperature per head, a bias by distance, a sink in the softmax's denominator
 // (see AttnParams); jv_attn_simt is the plain softmax form with values shaped like the keys.
 // n_splits == 0: every work item attends to its whole visible range and writes `out`.
 // n_splits > 0: work items are single tokens; part_o [n_work*Hq*n_splits*D] and part_ml
@@ -289,9 +304,11 @@ JV_EXPORT int jv_attn_simt_ex(const void* q, int q_stride, void* out, int out_st
                               const int* start_pos, const int* work, int n_work, int n_q_heads,
                               int n_kv_heads, int head_dim, int page_size, int num_pages, int window,
                               float scale, int split_size, int n_splits, int v_dim, int n_v_heads, int v_row,
-                              float score_cap, int sigmoid, const float* bias, int out_f32, int* status,
+                              float score_cap, int sigmoid, const float* bias, int out_f32, const float* head_scale,
+                              const float* dist_bias, int n_dist, const float* sink, int* status,
                               cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
+  if ((dist_bias != nullptr && n_dist < 1) || (sink != nullptr && sigmoid)) return JV_ERR_UNSUPPORTED;
   if (v_row <= 0) v_row = head_dim;
   if (n_v_heads <= 0) n_v_heads = n_kv_heads;
   if (v_dim <= 0) v_dim = v_row;
@@ -301,6 +318,7 @@ JV_EXPORT int jv_attn_simt_ex(const void* q, int q_stride, void* out, int out_st
   AttnParams p;
   p.n_v_heads = n_v_heads; p.v_row = v_row; p.score_cap = score_cap; p.sigmoid = sigmoid ? 1 : 0; p.bias = bias;
   p.out_f32 = out_f32 ? 1 : 0;
+  p.head_scale = head_scale; p.dist_bias = dist_bias; p.n_dist = n_dist; p.sink = sink;
   p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
   p.part_o = part_o; p.part_ml = part_ml; p.k_cache = k_cache; p.v_cache = v_cache;
   p.block_table = block_table; p.table_width = table_width; p.cu_seqlens = cu_seqlens;
@@ -357,5 +375,5 @@ JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_strid
   return jv_attn_simt_ex(q, q_stride, out, out_stride, dtype, part_o, part_ml, k_cache, v_cache, block_table,
                          table_width, cu_seqlens, start_pos, work, n_work, n_q_heads, n_kv_heads, head_dim, page_size,
                          num_pages, window, scale, split_size, n_splits, v_dim, n_kv_heads, head_dim, 0.f, 0, nullptr,
-                         0, status, stream);
+                         0, nullptr, nullptr, 0, nullptr, status, stream);
 }

@@ -1,9 +1,10 @@
 // Routing of a mixture of experts, all in 32-bit.
 //
 // jv_moe_route, one warp per token, from the router logits z = W_router x (a product made before it, with 32-bit
-// accumulation and a 32-bit result):  s = softmax(z) over all experts; with groups, a group's score is its largest s and only experts of the
+// accumulation and a 32-bit result):  s = softmax(z) over all experts, or sigmoid(z) of each (`scoring` 1); with groups, a
+// group's score is its largest s, or the sum of its two largest (`group_mode` 1), and only experts of the
 // `keep` best groups stay; the `top` largest s among those are chosen, largest first (lowest index on a tie);
-// weight = s (divided by the chosen scores' sum if `renorm`).
+// weight = s (divided by the chosen scores' sum plus `renorm_eps` if `renorm`), times `weight_scale`.
 //
 // jv_moe_align, one block: puts the (token, choice) pairs in the order of their experts, every expert's run
 // padded to a multiple of `tile` rows so that a row tile of the grouped products belongs to one expert:
@@ -19,7 +20,8 @@ constexpr int ROUTE_WARPS = 4;
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
     const float* __restrict__ z, int z_stride, int n, int experts, int top, int groups,
-    int keep, int renorm, int* __restrict__ ids, float* __restrict__ weights) {
+    int keep, int renorm, int scoring, int group_mode, float renorm_eps, float weight_scale,
+    int* __restrict__ ids, float* __restrict__ weights) {
   extern __shared__ float smem[];                 // [ROUTE_WARPS][experts] scores, [ROUTE_WARPS][groups] group scores
   pdl_trigger();
   pdl_wait();
@@ -30,21 +32,29 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
   float* gs = s + experts;
   for (int e = lane; e < experts; e += 32) s[e] = z[(size_t)t * z_stride + e];
   __syncwarp();
-  float mx = -INFINITY;
-  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, s[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < experts; e += 32) sum += expf(s[e] - mx);
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < experts; e += 32) s[e] = expf(s[e] - mx) / sum;
+  if (scoring == 1) {
+    for (int e = lane; e < experts; e += 32) s[e] = 1.f / (1.f + expf(-s[e]));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) sum += expf(s[e] - mx);
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < experts; e += 32) s[e] = expf(s[e] - mx) / sum;
+  }
   __syncwarp();
   const int per = experts / groups;
   if (groups > 1) {
     for (int g = lane; g < groups; g += 32) {
-      float b = -1.f;
-      for (int j = 0; j < per; ++j) b = fmaxf(b, s[g * per + j]);
-      gs[g] = b;
+      float b = -1.f, b2 = -1.f;                  // the largest and the second largest score of the group
+      for (int j = 0; j < per; ++j) {
+        const float v = s[g * per + j];
+        if (v > b) { b2 = b; b = v; }
+        else if (v > b2) b2 = v;
+      }
+      gs[g] = (group_mode == 1 && per > 1) ? b + b2 : b;
     }
     __syncwarp();
     // keep the best `keep` groups: a kept group's score is made negative minus one, so it is not found again
@@ -85,8 +95,13 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
     chosen_sum += bv;
     __syncwarp();
   }
-  if (renorm && lane == 0)
-    for (int it = 0; it < top; ++it) weights[(size_t)t * top + it] /= chosen_sum;
+  if (lane == 0) {
+    for (int it = 0; it < top; ++it) {
+      float w = weights[(size_t)t * top + it];
+      if (renorm) w /= (chosen_sum + renorm_eps);
+      weights[(size_t)t * top + it] = w * weight_scale;
+    }
+  }
 }
 
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int pairs, int top, int experts,
@@ -160,7 +175,8 @@ JV_EXPORT int jv_moe_gather_rows(const void* x, int dtype, int x_stride, const i
 
 // z: [n, experts] float rows of z_stride elements; ids: [n, top] int32; weights: [n, top] float.
 JV_EXPORT int jv_moe_route(const float* z, int z_stride, int n, int experts, int top, int groups, int keep, int renorm,
-                           int* ids, float* weights, cudaStream_t stream) {
+                           int scoring, int group_mode, float renorm_eps, float weight_scale, int* ids, float* weights,
+                           cudaStream_t stream) {
   if (n == 0) return JV_OK;
   if (experts < 1 || top < 1 || top > experts || groups < 1 || experts % groups || keep < 1 || keep > groups ||
       top > keep * (experts / groups))
@@ -169,7 +185,7 @@ JV_EXPORT int jv_moe_route(const float* z, int z_stride, int n, int experts, int
   if (smem > 48 * 1024) return JV_ERR_UNSUPPORTED;
   const int blocks = (n + ROUTE_WARPS - 1) / ROUTE_WARPS;
   return jv_launch(moe_route_kernel, dim3(blocks), dim3(ROUTE_WARPS * 32), smem, stream, z, z_stride, n, experts, top,
-                   groups, keep, renorm, ids, weights);
+                   groups, keep, renorm, scoring, group_mode, renorm_eps, weight_scale, ids, weights);
 }
 
 // ids: [pairs] experts of the (token, choice) pairs, pairs = n * top; sorted_token: [max_tiles * tile];

@@ -284,7 +284,7 @@ def _delta_parts(delta, h: torch.Tensor):
     """(tensor, parts, elements between parts) for a `delta` that is a tensor, a PartialSum or None."""
     if delta is None:
         return None, 1, 0
-    if isinstance(delta, PickedRows):
+    if isinstance(delta, (PickedRows, GatedDelta)):
         delta = delta.tensor()
     if isinstance(delta, PartialSum):
         parts = _cuda(delta.parts, "delta parts", torch.float32)
@@ -298,8 +298,11 @@ def _delta_parts(delta, h: torch.Tensor):
 
 
 def residual_add(h: torch.Tensor, delta) -> torch.Tensor:
-    """h += delta (a tensor or a PartialSum), the sum kept in float32."""
+    """h += delta (a tensor, a PartialSum or a gated delta), the sum kept in float32."""
     _cuda(h, "h", torch.float32)
+    if isinstance(delta, GatedDelta):
+        gated_add_dyt(h, delta)
+        return h
     delta, n_parts, part_stride = _delta_parts(delta, h)
     f = _fn("norm", "jv_residual_add", [c_void_p, c_void_p, c_int, c_longlong, c_int, c_longlong, c_void_p])
     _check(f(h.data_ptr(), delta.data_ptr(), _code(delta, "delta"), h.numel(), n_parts, part_stride, _stream()),
@@ -387,7 +390,8 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
               block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
               n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
               split_size: int = 0, n_splits: int = 0, v_dim: int = 0, score_cap: float = 0.0, sigmoid: bool = False,
-              bias: torch.Tensor | None = None) -> None:
+              bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
+              dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> None:
     """Paged causal attention on CUDA cores (csrc/attn_simt.cu).  `work` is [n_work, 2] int32
     (entry, first token of the tile); with `n_splits` > 0 the work items are single tokens
     whose keys are split into `n_splits` ranges of `split_size` positions.  `v_dim` > 0: only that many
@@ -397,7 +401,21 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     The value cache may have other heads and another row size than the key cache ([pages, page, value heads,
     value size]): key head g then reads value head g % value heads.  `score_cap` > 0 caps the scaled scores by
     cap * tanh(score / cap); `sigmoid` replaces the softmax by independent weights sigmoid(score + bias[query
-    head]); `out` may be float32 whatever the type of q."""
+    head]); `out` may be float32 whatever the type of q.  `head_scale` [query heads] multiplies the scaled scores of
+    its head; `dist_bias` [distances, query heads] is added to the score of a key that lies so many positions back
+    (the last row serves every larger distance); `sink` [query heads] adds exp(sink) once to the softmax's
+    denominator."""
+    for t, nm in ((head_scale, "head_scale"), (sink, "sink")):
+        if t is not None:
+            _cuda(t, nm, torch.float32)
+            if t.numel() != n_q_heads:
+                raise KernelError(f"attn_simt: {nm} holds one number per query head")
+    n_dist = 0
+    if dist_bias is not None:
+        _cuda(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != n_q_heads or dist_bias.shape[0] < 1:
+            raise KernelError("attn_simt: dist_bias is [distances, query heads]")
+        n_dist = dist_bias.shape[0]
     for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, q.dtype, contiguous=(nm != "q"))
     _cuda(out, "out", contiguous=False)
@@ -424,12 +442,14 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     f = _fn("attn_simt", "jv_attn_simt_ex", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-                                             c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p])
+                                             c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _code(q, "q"), _ptr(part_o), _ptr(part_ml),
              k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
              k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits), v_dim,
              n_v_heads, v_row, float(score_cap), 1 if sigmoid else 0, _ptr(bias), 1 if out.dtype != q.dtype else 0,
+             _ptr(head_scale), _ptr(dist_bias), n_dist, _ptr(sink),
              _status_ptr(q.device), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
@@ -570,7 +590,7 @@ def attn_finish(a: torch.Tensor, out: torch.Tensor, heads: int, value_dim: int, 
     return out
 
 
-UNARY_ACTIVATIONS = {"relu2": 0}       # relu(z)^2
+UNARY_ACTIVATIONS = {"relu2": 0, "gelu": 1, "tanh": 2}       # relu(z)^2, the exact (erf) gelu, tanh
 
 
 def unary_act(z: torch.Tensor, kind: str, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -1145,18 +1165,26 @@ def bmm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None)
 
 
 # ------------------------------------------------------------------- routed experts
-def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renorm: bool):
+ROUTER_SCORINGS = {"softmax": 0, "sigmoid": 1}
+GROUP_SCORES = {"max": 0, "top2_sum": 1}
+
+
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renorm: bool, scoring: str = "softmax",
+              group_score: str = "max", renorm_eps: float = 0.0, weight_scale: float = 1.0):
     """(ids [n, top] int32, weights [n, top] float32) from the router logits [n, experts] float32: softmax over all
-    experts, group-limited choice of the `top` largest, largest first (csrc/moe_route.cu)."""
+    experts or a sigmoid of each, group-limited choice of the `top` largest, largest first (csrc/moe_route.cu); a
+    group scores as its best expert or as the sum of its two best; the chosen scores are divided by their sum
+    (+ `renorm_eps`) if `renorm`, and multiplied by `weight_scale`."""
     _cuda(logits, "router logits", torch.float32, contiguous=False)
     n, experts = logits.shape
     if logits.stride(1) != 1:
         raise KernelError("router logits need unit column stride")
     ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    f = _fn("moe_route", "jv_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                          c_void_p])
-    _check(f(logits.data_ptr(), logits.stride(0), n, experts, top, groups, keep, 1 if renorm else 0, ids.data_ptr(),
+    f = _fn("moe_route", "jv_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                          c_float, c_void_p, c_void_p, c_void_p])
+    _check(f(logits.data_ptr(), logits.stride(0), n, experts, top, groups, keep, 1 if renorm else 0,
+             ROUTER_SCORINGS[scoring], GROUP_SCORES[group_score], float(renorm_eps), float(weight_scale), ids.data_ptr(),
              weights.data_ptr(), _stream()), "moe_route")
     return ids, weights
 
@@ -1275,6 +1303,220 @@ def token_gate(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offse
     _check(f(z.data_ptr(), _code(z, "z"), _code(g, "g"), tokens.data_ptr(), table.data_ptr(), _code(table, "table"), width, offset,
              vocab, g.data_ptr(), n, dim, _status_ptr(z.device), _stream()), "token_gate")
     return g
+
+
+# ------------------------------------------------- clamped gate, logit cap (csrc/activation.cu)
+def glu_clamped(gu: torch.Tensor, limit: float, slope: float = 1.702) -> torch.Tensor:
+    """act = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), from rows
+    [gate | up] (32-bit arithmetic)."""
+    _cuda(gu, "gate|up")
+    n, two = gu.shape
+    if two % 2:
+        raise KernelError("glu_clamped: rows hold gate and up columns of equal number")
+    act = torch.empty((n, two // 2), dtype=gu.dtype, device=gu.device)
+    f = _fn("activation", "jv_glu_clamped", [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(gu.data_ptr(), act.data_ptr(), _code(gu, "gate|up"), n, two // 2, float(limit), float(slope), _stream()),
+           "glu_clamped")
+    return act
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), in place on float32 values."""
+    _cuda(x, "x", torch.float32)
+    f = _fn("activation", "jv_softcap", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(x.data_ptr(), x.numel(), float(cap), _stream()), "softcap")
+    return x
+
+
+# ------------------------------------------ dynamic-tanh norm and gated residual (csrc/dyt.cu)
+class GatedDelta:
+    """A branch output that enters the stream through a gate: the sum is h += sigmoid(z + bias) * y, element by
+    element, in 32-bit.  `y` [n, hidden] (compute type or float32), `z` [n, hidden] (possibly a column range of a
+    wider tensor), `bias` [hidden].  `gated_add_dyt` adds it as it forms the next norm; `residual_add` and
+    `tensor()` serve any other reader."""
+
+    def __init__(self, y: torch.Tensor, z: torch.Tensor, bias: torch.Tensor):
+        self.y, self.z, self.bias = y, z, bias
+
+    @property
+    def shape(self):
+        return self.y.shape
+
+    @property
+    def device(self):
+        return self.y.device
+
+    def tensor(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        out = torch.zeros(tuple(self.shape), dtype=torch.float32, device=self.device)
+        gated_add_dyt(out, self)
+        return out if dtype == torch.float32 else out.to(dtype)
+
+
+def gated_add_dyt(h: torch.Tensor, delta=None, alpha: float = 0.0, weight: torch.Tensor | None = None,
+                  bias: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                  rows: torch.Tensor | None = None):
+    """h += delta (a tensor, a `GatedDelta`, or anything with `.tensor()`), then, with `weight`, the dynamic-tanh norm
+    x = tanh(alpha * h) * weight + bias of every row (of `rows` only, if given: h then stays as it is), in one pass."""
+    _cuda(h, "h", torch.float32)
+    n_total, hidden = h.shape
+    y = z = zb = None
+    z_stride = 0
+    if isinstance(delta, GatedDelta):
+        y, z, zb = delta.y, delta.z, delta.bias
+        _cuda(z, "gate", contiguous=False); _cuda(zb, "gate bias")
+        if z.shape != h.shape or z.stride(1) != 1 or zb.numel() != hidden:
+            raise KernelError("gated residual: the gate has the stream's shape, its bias one row")
+        z_stride = z.stride(0)
+    elif delta is not None:
+        y = delta if isinstance(delta, torch.Tensor) else delta.tensor()
+    if y is not None:
+        _cuda(y, "delta")
+        if y.shape != h.shape:
+            raise KernelError("delta and h differ in shape")
+    out = None
+    if weight is not None:
+        _cuda(weight, "weight"); _cuda(bias, "bias", weight.dtype)
+        if weight.numel() != hidden or bias.numel() != hidden:
+            raise KernelError("dynamic-tanh norm: weight and bias have one row's size")
+        if zb is not None and zb.dtype != weight.dtype:
+            zb = zb.to(weight.dtype)
+        n_out = n_total if rows is None else rows.numel()
+        out = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
+    elif rows is not None:
+        raise KernelError("gated_add_dyt: rows are for the norm")
+    else:
+        n_out = n_total
+        if y is None:
+            return None
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+    w_code = _code(weight, "weight") if weight is not None else (_code(zb, "gate bias") if zb is not None else 0)
+    f = _fn("dyt", "jv_gated_add_dyt", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_float,
+                                        c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(h.data_ptr(), _ptr(rows), _ptr(y), 0 if y is None else _code(y, "delta"), _ptr(z),
+             0 if z is None else _code(z, "gate"), z_stride, _ptr(zb), float(alpha), _ptr(weight), _ptr(bias), w_code,
+             _ptr(out), 0 if out is None else _code(out, "out"), n_out, n_total, hidden, _status_ptr(h.device), _stream()),
+           "gated_add_dyt")
+    return out
+
+
+def add_row(h: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+    """h[n, :] += vec for every row of the float32 stream."""
+    _cuda(h, "h", torch.float32); _cuda(vec, "vec")
+    if vec.numel() != h.shape[1]:
+        raise KernelError("add_row: the vector has one row's size")
+    f = _fn("dyt", "jv_add_row", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(h.data_ptr(), vec.data_ptr(), _code(vec, "vec"), h.shape[0], h.shape[1], _stream()), "add_row")
+    return h
+
+
+def norm_mean2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float,
+               coef: float = 0.5) -> torch.Tensor:
+    """coef * (unit(a) * wa + unit(b) * wb) as float32, unit(y) = y / sqrt(mean(y^2) + eps) over a row."""
+    _cuda(a, "a"); _cuda(b, "b", a.dtype); _cuda(wa, "wa"); _cuda(wb, "wb", wa.dtype)
+    n, hidden = a.shape
+    if b.shape != a.shape or wa.numel() != hidden or wb.numel() != hidden:
+        raise KernelError("norm_mean2: shapes do not fit")
+    out = torch.empty((n, hidden), dtype=torch.float32, device=a.device)
+    f = _fn("dyt", "jv_norm_mean2", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
+                                     c_float, c_void_p])
+    _check(f(a.data_ptr(), b.data_ptr(), _code(a, "a"), wa.data_ptr(), wb.data_ptr(), _code(wa, "wa"), out.data_ptr(), n,
+             hidden, float(eps), float(coef), _stream()), "norm_mean2")
+    return out
+
+
+# ------------------------------------------------ matrix states carried from token to token (csrc/recurrent.cu)
+SCAN_MAX_KEY = 256
+
+
+def delta_prepare(proj: torch.Tensor, r_off: int, k_off: int, a_off: int, zw: torch.Tensor, a_bias: torch.Tensor,
+                  w_bias: torch.Tensor, heads: int, dim: int) -> torch.Tensor:
+    """Per token and head the vectors (r, k, w, u, b) of the generalized delta rule as float32 [n, heads, 5, dim]:
+    w = exp(-e^(-1/2) sigmoid(zw + w_bias)), u = k / sqrt(|k|^2 + 1e-6), b = sigmoid(z_a + a_bias) * u."""
+    _cuda(proj, "proj", contiguous=False); _cuda(zw, "zw", proj.dtype, contiguous=False)
+    _cuda(a_bias, "a_bias"); _cuda(w_bias, "w_bias", a_bias.dtype)
+    n = proj.shape[0]
+    if proj.stride(1) != 1 or zw.stride(1) != 1 or zw.shape != (n, heads * dim) or \
+            max(r_off, k_off, a_off) + heads * dim > proj.shape[1] or a_bias.numel() != heads * dim or \
+            w_bias.numel() != heads * dim:
+        raise KernelError("delta_prepare: shapes do not fit")
+    packed = torch.empty((n, heads, 5, dim), dtype=torch.float32, device=proj.device)
+    f = _fn("recurrent", "jv_delta_prepare", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong,
+                                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(proj.data_ptr(), _code(proj, "proj"), proj.stride(0), r_off, k_off, a_off, zw.data_ptr(), zw.stride(0),
+             a_bias.data_ptr(), w_bias.data_ptr(), _code(a_bias, "a_bias"), packed.data_ptr(), n, heads, dim, _stream()),
+           "delta_prepare")
+    return packed
+
+
+def memory_gates(proj: torch.Tensor, q_off: int, k_off: int, i_off: int, f_off: int, i_bias: torch.Tensor,
+                 f_bias: torch.Tensor, cap: float, q_scale: float, state_n: torch.Tensor, state_m: torch.Tensor,
+                 cu_seqlens: torch.Tensor, slots: torch.Tensor, n_entries: int, heads: int, dim: int) -> torch.Tensor:
+    """The gates of a matrix memory with exponential gating, scanned over every entry's tokens: updates the normaliser
+    `state_n` [slots, heads * dim] and the running maximum `state_m` [slots, heads] (views of the state rows, equal
+    row stride) and returns float32 [n, heads, 3, dim]: the query over its denominator, the key times its input
+    gate, the decay."""
+    _cuda(proj, "proj", contiguous=False); _cuda(i_bias, "i_bias"); _cuda(f_bias, "f_bias", i_bias.dtype)
+    _cuda(state_n, "state_n", torch.float32, contiguous=False); _cuda(state_m, "state_m", torch.float32, contiguous=False)
+    _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(slots, "slots", torch.int32)
+    n = proj.shape[0]
+    if proj.stride(1) != 1 or state_n.stride(0) != state_m.stride(0) or state_n.stride(1) != 1 or \
+            state_n.shape[1] != heads * dim or state_m.shape[1] != heads or dim > SCAN_MAX_KEY:
+        raise KernelError("memory_gates: shapes do not fit")
+    packed = torch.empty((n, heads, 3, dim), dtype=torch.float32, device=proj.device)
+    f = _fn("recurrent", "jv_memory_gates", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                             c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                             c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(proj.data_ptr(), _code(proj, "proj"), proj.stride(0), q_off, k_off, i_off, f_off, i_bias.data_ptr(),
+             f_bias.data_ptr(), _code(i_bias, "i_bias"), float(cap), float(q_scale), packed.data_ptr(), state_n.data_ptr(),
+             state_m.data_ptr(), state_n.stride(0), cu_seqlens.data_ptr(), slots.data_ptr(), state_n.shape[0], n_entries,
+             heads, dim, _status_ptr(proj.device), _stream()), "memory_gates")
+    return packed
+
+
+def state_scan(packed: torch.Tensor, v: torch.Tensor, v_off: int, state: torch.Tensor, cu_seqlens: torch.Tensor,
+               slots: torch.Tensor, n_entries: int, value_dim: int) -> torch.Tensor:
+    """S <- diag(w) S - b (u^T S) + k v^T and o = S^T r, token after token of every entry, for the per-head states
+    `state` [slots, >= heads * dim * value_dim] float32 (a view of the state rows); `packed` [n, heads, 5 or 3, dim]
+    holds (r, k, w, u, b) or, without the removal term, (r, k, w); the values are columns `v_off`.. of the rows of
+    `v`.  Returns o [n, heads * value_dim] float32."""
+    _cuda(packed, "packed", torch.float32); _cuda(v, "v", contiguous=False)
+    _cuda(state, "state", torch.float32, contiguous=False)
+    _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(slots, "slots", torch.int32)
+    n, heads, nv, dim = packed.shape
+    if nv not in (3, 5) or v.shape[0] != n or v.stride(1) != 1 or v_off + heads * value_dim > v.shape[1] or \
+            state.stride(1) != 1 or state.shape[1] < heads * dim * value_dim or dim > SCAN_MAX_KEY:
+        raise KernelError("state_scan: shapes do not fit")
+    out = torch.empty((n, heads * value_dim), dtype=torch.float32, device=packed.device)
+    f = _fn("recurrent", "jv_state_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p,
+                                           c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                           c_void_p])
+    _check(f(packed.data_ptr(), 1 if nv == 5 else 0, v.data_ptr(), _code(v, "v"), v.stride(0), v_off, out.data_ptr(),
+             state.data_ptr(), state.stride(0), cu_seqlens.data_ptr(), slots.data_ptr(), state.shape[0], n_entries, heads,
+             dim, value_dim, _status_ptr(packed.device), _stream()), "state_scan")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, heads: int,
+                   value_dim: int, eps: float) -> torch.Tensor:
+    """Each head of `o` [n, heads * value_dim] float32 divided by its root mean square, times `weight` [heads *
+    value_dim], times sigmoid(gate) (rows of `out`'s type, possibly a column range), written to `out` (possibly a
+    column range)."""
+    _cuda(o, "o", torch.float32); _cuda(weight, "weight"); _cuda(out, "out", contiguous=False)
+    n = o.shape[0]
+    if o.shape[1] != heads * value_dim or out.shape != o.shape or out.stride(1) != 1 or weight.numel() != o.shape[1]:
+        raise KernelError("head_norm_gate: shapes do not fit")
+    g_stride = 0
+    if gate is not None:
+        _cuda(gate, "gate", out.dtype, contiguous=False)
+        if gate.shape != o.shape or gate.stride(1) != 1:
+            raise KernelError("head_norm_gate: the gate has the heads' shape")
+        g_stride = gate.stride(0)
+    f = _fn("recurrent", "jv_head_norm_gate", [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_longlong,
+                                               c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(o.data_ptr(), weight.data_ptr(), _code(weight, "weight"), _ptr(gate), g_stride, out.data_ptr(),
+             _code(out, "out"), out.stride(0), n, heads, value_dim, float(eps), _stream()), "head_norm_gate")
+    return out
 
 
 # ------------------------------------------------------------------------- sampling

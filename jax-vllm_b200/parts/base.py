@@ -9,7 +9,8 @@ which model it sits in.
     Position        table(device) -> tensor handed to the mixer's kernels (e.g. inverse
                     frequencies); rot_dim
     Mixer           forward(x, step, cache) -> y        x, y: [tokens, hidden] compute dtype
-                    cache_need() -> PagedKVNeed | FixedStateNeed | None
+                    cache_need() -> PagedKVNeed | FixedStateNeed | None, or a tuple of those (the mixer then
+                                    gets a tuple of cache views in the same order)
                     tile_classes() -> work lists it wants for entries of several tokens: triples
                                       (tokens per tile, least new tokens, one more than the most)
     FeedForward     forward(x, step) -> y
@@ -26,10 +27,18 @@ import torch
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """A tensor a part expects from the model folder."""
+    """A tensor a part expects from the model folder.  An axis given as -1 has whatever size the folder's tensor has
+    (the part reads it when it binds); random weights give it `FREE_AXIS`."""
     shape: tuple
     kind: str = "matrix"        # "matrix", "vector" (norm weights and the like) or "table" (integers)
     init: str = "normal"        # random mode: "normal" = N(0, 0.02); "ones_normal" = 1 + N(0, 0.1)
+
+
+FREE_AXIS = 16
+
+
+def shape_fits(got, want) -> bool:
+    return len(got) == len(want) and all(w == g or (w == -1 and g >= 1) for g, w in zip(got, want))
 
 
 @dataclass(frozen=True)

@@ -15,46 +15,110 @@ import torch
 
 from .. import ops
 from ..ops import trace_range
-from .base import Part
+from .base import Part, TensorSpec
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TOKEN_INPUTS, build, register_block
 
 
 class PreNormBlock(Part):
+    """h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))   (the feed-forward is optional)
+
+    With `residual_gates` each sublayer's result enters the stream through a gate, element by element:
+    h = h + sigmoid(W_g x + b_g) * sublayer(x), x being the sublayer's input.  The gate's product reads the same x
+    as the sublayer, so where the sublayer offers its input product (`in_weight`) the gate's matrix is stacked under
+    it and one product serves both; the sum itself is made by the norm that follows (`ops.GatedDelta`)."""
+
     def __init__(self, spec, prefix, ctx):
         p = spec.prefix
-        self.spec = spec
+        self.spec, self.ctx = spec, ctx
         self.mixer_norm = build(NORMS, "norm", spec.mixer_norm, p, ctx)
         self.mixer = build(MIXERS, "mixer", spec.mixer, p, ctx)
-        self.ffn_norm = build(NORMS, "norm", spec.ffn_norm, p, ctx)
-        self.feed_forward = build(FEED_FORWARDS, "feed-forward", spec.feed_forward, p, ctx)
+        self.ffn_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ffn_norm = build(NORMS, "norm", spec.ffn_norm, p, ctx)
+            self.feed_forward = build(FEED_FORWARDS, "feed-forward", spec.feed_forward, p, ctx)
         if spec.cache_from is not None:
             if not hasattr(self.mixer, "writes_cache"):
                 raise ValueError(f"{p}: this mixer cannot read another layer's cache")
             self.mixer.writes_cache = False
+        gates = spec.residual_gates
+        self.gate_names = None if gates is None else tuple(f"{p}.{g}" for g in gates)
+        self.gate_w = [None, None]        # per sublayer: the gate's matrix alone, or None where it is stacked
+        self.gate_b = [None, None]
+        self.packed = [None, None]        # per sublayer: its input matrix with the gate's stacked under it
+        if gates is not None:
+            self.kernels = ("dyt", "gemm_simt")
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if part is not None)
 
     def tensor_specs(self):
         out = {}
         for part in self.parts():
             out.update(part.tensor_specs())
+        if self.gate_names is not None:
+            W = self.spec.mixer_norm.size
+            for name in self.gate_names[:2 if self.feed_forward is not None else 1]:
+                out[name] = TensorSpec((W, W))
+                out[f"{name}.b"] = TensorSpec((W,), kind="vector", init="normal")
         return out
 
     def bind(self, tensors):
         for part in self.parts():
             part.bind(tensors)
+        if self.gate_names is None:
+            return
+        subs = (self.mixer, self.feed_forward)
+        for i, sub in enumerate(subs):
+            if sub is None:
+                continue
+            w = self.compute_weight(tensors[self.gate_names[i]], self.ctx).contiguous()
+            self.gate_b[i] = tensors[f"{self.gate_names[i]}.b"].contiguous()
+            self.gate_w[i], self.packed[i] = w, None
+            ready = hasattr(sub, "forward_projected") if i == 0 else hasattr(sub, "from_projection")
+            if ready and sub.in_weight().dtype == w.dtype:
+                self.packed[i] = torch.cat([sub.in_weight(), w], dim=0).contiguous()
+
+    def _mixer(self, x, step, cache):
+        """The mixer's result, and the pre-activation of its gate (or None)."""
+        dt = self.ctx.dtype
+        if self.gate_names is None:
+            return self.mixer.forward(x, step, cache), None
+        if self.packed[0] is None:
+            return _plain(self.mixer.forward(x, step, cache)), ops.linear(x, self.gate_w[0], dt)
+        row = ops.linear(x, self.packed[0], dt)
+        rm = self.mixer.in_rows
+        return self.mixer.forward_projected(row[:, :rm], step, cache), row[:, rm:]
+
+    def _feed_forward(self, x, step):
+        dt = self.ctx.dtype
+        ff = self.feed_forward
+        if self.gate_names is None:
+            return ff.forward(x, step), None
+        if self.packed[1] is None:
+            return _plain(ff.forward(x, step)), ops.linear(x, self.gate_w[1], dt)
+        row = ops.linear(x, self.packed[1], dt)
+        rm = ff.in_rows
+        return ops.linear(ff.from_projection(row[:, :rm], step), ff.out_weight(), dt), row[:, rm:]
 
     def forward(self, h, delta, step, cache):
         step.stream_copy = None
         with trace_range("mixer_norm"):
             x = self.mixer_norm.norm(h, delta)
         with trace_range("mixer"):
-            a = self.mixer.forward(x, step, cache)
+            a, z = self._mixer(x, step, cache)
+            if z is not None:
+                a = ops.GatedDelta(a, z, self.gate_b[0])
+        if self.feed_forward is None:
+            return h, a
         with trace_range("ffn_norm"):
             x = self.ffn_norm.norm(h, a)
         with trace_range("feed_forward"):
-            return h, self.feed_forward.forward(x, step)
+            y, z = self._feed_forward(x, step)
+            return h, (y if z is None else ops.GatedDelta(y, z, self.gate_b[1]))
+
+
+def _plain(y):
+    return y if isinstance(y, torch.Tensor) else y.tensor()
 
 
 register_block("pre_norm", PreNormBlock)

@@ -1,4 +1,4 @@
-"""A feed-forward without a gate: down(act(up(x))), act = relu(z)^2, no bias.
+"""A feed-forward without a gate: down(act(up(x))), act = relu(z)^2 or the exact gelu (by name), no bias.
 
 Like the attention mixers it offers its two products to an arrangement that packs them with another part's
 (`in_weight`, `from_projection`, `out_weight`)."""

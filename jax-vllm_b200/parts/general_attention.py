@@ -30,6 +30,22 @@ from .base import PagedKVNeed, Part, TensorSpec
 from .registry import POSITIONS, build, register_mixer
 
 
+def distance_buckets(buckets: int, saturate: int) -> list:
+    """The row of a learned distance-bias table [buckets, heads] that serves the key `n` positions back, for n = 0 ..
+    `saturate`: exact up to half the table, n itself; beyond, logarithmic steps, half + floor(ln(n / half) /
+    ln(saturate / half) * (buckets - half)), capped at the last row, which every distance from `saturate` on shares."""
+    half = buckets // 2
+    if half < 1 or saturate <= half:
+        raise ValueError(f"distance bias: {buckets} buckets need at least 2 rows and a largest distance beyond {half}")
+    out = []
+    for n in range(saturate + 1):
+        if n < half:
+            out.append(n)
+        else:
+            out.append(min(buckets - 1, half + int(math.floor(math.log(n / half) / math.log(saturate / half) * (buckets - half)))))
+    return out
+
+
 class GeneralAttention(Part):
     kernels = ("attn_prepare", "attn_simt", "attn_finish", "gemm_simt")
     FOREVER = 1 << 30
@@ -60,14 +76,18 @@ class GeneralAttention(Part):
         # tcgen05 kernels for heads of 128, mma.sync for 16/32/64, in bfloat16).  Every other bfloat16 mixer with
         # sizes in steps of 16 takes the tensor-core kernel compiled for its pair of sizes; the rest, and 32-bit,
         # the CUDA-core kernel.
+        # a temperature per head, a bias by distance and a sink are options of the CUDA-core kernel
+        self.extras = spec.head_temperature or spec.distance_bias is not None or spec.sink
+        if self.extras and (spec.twin is not None or (spec.sink and spec.weights != "softmax")):
+            raise ValueError("head temperature, distance bias and sink are built for one softmax map")
         plain = (spec.twin is None and spec.weights == "softmax" and not spec.score_cap and self.hv == self.hk
-                 and self.dv == self.d)
+                 and self.dv == self.d and not self.extras)
         self.plain = self.general = None
         if plain and ops.attn_mma_supports(ctx.dtype, self.d):
             self.plain = Attention(AttentionSpec(spec.hidden_size, self.hq, self.hk, self.d, spec.scale, prefix=""),
                                    self.prefix, ctx)
             self.kernels += tuple(k for k in self.plain.kernels if k not in self.kernels and k != "rope_kv")
-        elif ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
+        elif not self.extras and ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
             self.general = ops.attn_general_mma_library(self.d, self.dv)
             self.kernels += (self.general,)
         # sigmoid weights on heads of 128: prompt portions that fill a 128-row tile go to the tcgen05 kernel
@@ -76,6 +96,7 @@ class GeneralAttention(Part):
         if self.sigmoid_tiles:
             self.kernels += ("attn_tcgen05",)
         self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
+        self.head_scale = self.dist_bias = self.sink = None
         self.lam = 0.0
         # columns of the packed projection
         self.k_off = self.hq * self.d
@@ -87,7 +108,7 @@ class GeneralAttention(Part):
 
     # -------------------------------------------------------------------- weights
     def _names(self):
-        keys = ("q", "k", "v", "g", "o", "q_norm", "k_norm", "bias")
+        keys = ("q", "k", "v", "g", "o", "q_norm", "k_norm", "bias", "temp", "rel", "sink")
         return {k: f"{self.prefix}.{n}" for k, n in zip(keys, self.spec.names)}
 
     def tensor_specs(self):
@@ -107,6 +128,13 @@ class GeneralAttention(Part):
         if s.twin is not None:
             for name in s.twin.names:
                 specs[f"{self.prefix}.{name}"] = TensorSpec((self.d,), kind="vector", init="normal")
+        if s.head_temperature:
+            specs[n["temp"]] = TensorSpec((self.h,), kind="vector", init="ones_normal")
+        if s.distance_bias is not None:
+            rows = s.distance_bias[0]
+            specs[n["rel"]] = TensorSpec((-1 if rows is None else int(rows), self.h), kind="vector", init="normal")
+        if s.sink:
+            specs[n["sink"]] = TensorSpec((self.h,), kind="vector", init="normal")
         return specs
 
     def _maps_first(self, w: torch.Tensor, heads: int) -> torch.Tensor:
@@ -133,6 +161,15 @@ class GeneralAttention(Part):
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
         if s.score_bias:
             self.bias = tensors[n["bias"]].to(torch.float32).contiguous()
+        if s.head_temperature:
+            self.head_scale = tensors[n["temp"]].to(torch.float32).contiguous()
+        if s.distance_bias is not None:
+            # the table by distance, not by bucket: the kernel indexes it with min(distance, last row)
+            rel = tensors[n["rel"]].to(torch.float32)
+            rows = distance_buckets(rel.shape[0], int(s.distance_bias[1]))
+            self.dist_bias = rel[torch.tensor(rows, device=rel.device)].contiguous()
+        if s.sink:
+            self.sink = tensors[n["sink"]].to(torch.float32).contiguous()
         if s.twin is not None:
             lq1, lk1, lq2, lk2 = (tensors[f"{self.prefix}.{name}"].double() for name in s.twin.names)
             self.lam = math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + float(s.twin.offset)
@@ -169,6 +206,12 @@ class GeneralAttention(Part):
         self.from_projection(row, step, cache, heads)
         return ops.linear(heads, self.w_o, dt, parts_ok=True)
 
+    def forward_projected(self, row, step, cache):
+        """From the packed projection to the mixer's output, as one tensor."""
+        heads = torch.empty((step.n_tokens, self.heads_out), dtype=self.ctx.dtype, device=row.device)
+        self.from_projection(row, step, cache, heads)
+        return ops.linear(heads, self.w_o, self.ctx.dtype)
+
     def from_projection(self, row, step, cache, out):
         """`row` [n, in_rows] (the packed projection, possibly a column range of a wider tensor) -> the heads
         before the output projection, written to `out` [n, heads * value_dim] (possibly a column range)."""
@@ -200,6 +243,8 @@ class GeneralAttention(Part):
             return self.plain.attend(q, a, step, cache, table)
         common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)
         extra = dict(score_cap=s.score_cap or 0.0, sigmoid=s.weights == "sigmoid", bias=self.bias)
+        if self.extras:
+            extra.update(head_scale=self.head_scale, dist_bias=self.dist_bias, sink=self.sink)
         if self.general is not None:
             def kernel(work, n_work, **split):
                 ops.attn_general_mma(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, s.scale, **split, **extra)

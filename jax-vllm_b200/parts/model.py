@@ -25,6 +25,8 @@ class Model(Part):
         # earlier place at which the layer it names ran.
         self.order = tuple(spec.run_order())
         self.reinject = frozenset(spec.reinject)
+        self.position_table = self.pass_table = None
+        self.pass_rows = dict(spec.pass_vectors[1]) if spec.pass_vectors is not None else {}
         self.place_cache = []
         self.place_names = [f"layer {i}" if self.order.count(i) == 1 else f"layer {i} (place {k})"
                             for k, i in enumerate(self.order)]
@@ -39,6 +41,11 @@ class Model(Part):
     def tensor_specs(self):
         s = self.spec
         out = {s.embedding_name: TensorSpec((s.vocab_size, s.hidden_size))}
+        if s.position_table_name is not None:
+            out[s.position_table_name] = TensorSpec((s.max_position, s.hidden_size))
+        if s.pass_vectors is not None:
+            rows = 1 + max(row for _, row in s.pass_vectors[1])
+            out[s.pass_vectors[0]] = TensorSpec((rows, s.hidden_size), kind="vector", init="normal")
         for layer in self.layers:
             out.update(layer.tensor_specs())
         out.update(self.final_norm.tensor_specs())
@@ -54,6 +61,10 @@ class Model(Part):
     def bind(self, tensors):
         s = self.spec
         self.embedding = tensors[s.embedding_name].contiguous()
+        if s.position_table_name is not None:
+            self.position_table = tensors[s.position_table_name].contiguous()
+        if s.pass_vectors is not None:
+            self.pass_table = tensors[s.pass_vectors[0]].contiguous()
         for layer in self.layers:
             layer.bind(tensors)
         self.final_norm.bind(tensors)
@@ -62,6 +73,11 @@ class Model(Part):
 
     def kernels(self):
         names = {"embed", "norm", "gemm_simt"}
+        names.update(getattr(self.final_norm, "kernels", ()))
+        if self.pass_table is not None or self.spec.pass_vectors is not None:
+            names.add("dyt")
+        if self.spec.logit_softcap:
+            names.add("activation")
         if self.ctx.dtype == torch.bfloat16:
             names.update(("linear_skinny", "linear_stream"))
         for layer in self.layers:
@@ -99,6 +115,8 @@ class Model(Part):
         it (for comparing a model layer by layer; it costs a pass over the stream per layer)."""
         with ops.trace_range("embedding"):
             h = ops.embed_gather(self.embedding, step.token_ids)
+            if self.position_table is not None:      # a learned vector per position (a position beyond the table sets the
+                ops.embed_gather(self.position_table, step.positions, out=h, accumulate=True)   # status word)
         delta = None
         step.stream_copy = None
         for k, i in enumerate(self.order):
@@ -109,6 +127,12 @@ class Model(Part):
                     delta = None
                 step.stream_copy = None
                 ops.embed_gather(self.embedding, step.token_ids, out=h, accumulate=True)
+            if k in self.pass_rows:
+                if delta is not None:
+                    ops.residual_add(h, delta)
+                    delta = None
+                step.stream_copy = None
+                ops.add_row(h, self.pass_table[self.pass_rows[k]])
             with ops.trace_range(self.place_names[k]):
                 h, delta = self.layers[i].forward(h, delta, step, caches[self.place_cache[k]])
             if tap is not None:
@@ -118,4 +142,7 @@ class Model(Part):
         with ops.trace_range("final_norm"):
             x = self.final_norm.gather(h, delta, step.logit_rows)
         with ops.trace_range("lm_head"):
-            return ops.linear(x, self.lm_head, torch.float32)
+            logits = ops.linear(x, self.lm_head, torch.float32)
+            if self.spec.logit_softcap:
+                ops.softcap_(logits, self.spec.logit_softcap)
+            return logits

@@ -33,3 +33,37 @@ class RMSNorm(Part):
 
 
 register_norm("rmsnorm", RMSNorm)
+
+
+class DynamicTanh(Part):
+    """y = tanh(alpha * h) * weight + bias, element by element in 32-bit: no mean, no variance.  Tensors `<name>`
+    (weight), `<name>.b` (bias) and `<name>.alpha` (one number).  `eps` of the spec is not used.  The residual sum
+    before it, plain or through a gate (`ops.GatedDelta`), is made in the same pass (csrc/dyt.cu)."""
+
+    kernels = ("dyt",)
+
+    def __init__(self, spec, prefix, ctx):
+        self.size = spec.size
+        self.name = f"{prefix}.{spec.name}" if prefix else spec.name
+        self.ctx = ctx
+        self.weight = self.bias = None
+        self.alpha = 0.0
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.size,), kind="vector", init="ones_normal"),
+                f"{self.name}.b": TensorSpec((self.size,), kind="vector", init="normal"),
+                f"{self.name}.alpha": TensorSpec((), kind="vector", init="ones_normal")}
+
+    def bind(self, tensors):
+        self.weight = tensors[self.name].contiguous()
+        self.bias = tensors[f"{self.name}.b"].to(self.weight.dtype).contiguous()
+        self.alpha = float(tensors[f"{self.name}.alpha"].float().item())
+
+    def norm(self, h, delta=None):
+        return ops.gated_add_dyt(h, delta, self.alpha, self.weight, self.bias, self.ctx.dtype)
+
+    def gather(self, h, delta, rows):
+        return ops.gated_add_dyt(h, delta, self.alpha, self.weight, self.bias, self.ctx.dtype, rows=rows)
+
+
+register_norm("dyt", DynamicTanh)

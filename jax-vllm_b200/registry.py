@@ -57,6 +57,9 @@ def _register_builtin() -> None:
     from .models.loselix import ARCHITECTURE as LOSELIX, LoselixConfig
 
     register_architecture(LOSELIX, LoselixConfig)
+    from .models.nufapel import ARCHITECTURE as NUFAPEL, NufapelConfig
+
+    register_architecture(NUFAPEL, NufapelConfig)
 
 
 _register_builtin()

@@ -14,6 +14,8 @@ from pathlib import Path
 
 import torch
 
+from ..parts.base import shape_fits
+
 
 class WeightError(ValueError):
     """The folder's tensors do not fit the model.  `.missing`, `.unexpected` and `.wrong_shape`
@@ -89,7 +91,7 @@ def check(folder, index, specs: dict, optional=()) -> None:
         if n not in index:
             continue
         _, shape, dt = index[n]
-        if tuple(shape) != tuple(spec.shape):
+        if not shape_fits(tuple(shape), tuple(spec.shape)):
             wrong_shape.append((n, shape, spec.shape))
         is_int = dt.upper().startswith(("I", "U", "BOOL"))
         if (spec.kind == "table") != is_int:

@@ -14,6 +14,8 @@ from pathlib import Path
 
 import torch
 
+from ..parts.base import FREE_AXIS
+
 MATRIX_STD = 0.02
 NORM_STD = 0.1
 
@@ -26,9 +28,10 @@ def tensor_seed(seed: int, name: str) -> int:
 def random_tensor(name: str, spec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(tensor_seed(seed, name))
+    shape = tuple(FREE_AXIS if d == -1 else d for d in spec.shape)
     if spec.kind == "table":
-        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
-    z = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+        return torch.zeros(shape, dtype=torch.int32, device=device)
+    z = torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
     if spec.init == "ones_normal":
         z = 1.0 + NORM_STD * z
     else:
