@@ -690,6 +690,8 @@ def design(name: str, layers, sizes, steps, warmup) -> int:
     from jax_vllm_b200 import random_model, registry
     if name == "loselix":
         return design_loselix(layers or 3, sizes, steps, warmup)
+    if name == "nufapel":
+        return design_nufapel(layers or 3, sizes, steps, warmup)
     if name != "guronex":
         print(f"bench.py: no design {name!r}")
         return 2
@@ -752,6 +754,168 @@ def design_loselix(layers, sizes, steps, warmup) -> int:
     return 0
 
 
+# ------------------------------------------------------------------ the Nufapel design beside Loselix
+# Layer sizes for `--design nufapel`: three layers (attention with a distance bias and a sink beside a matrix memory,
+# over a dense feed-forward; a delta-rule layer over routed experts; the pair again over routed experts), beside three
+# Loselix softmax-attention layers of equal width, heads and feed-forward work per token.  "w2k": the width of a
+# 1B-class model, a memory of 8 heads of 128 x 256 and delta heads of 64; "w4k": an 8B-class width, a memory of 8 heads
+# of 256 x 512 (the sizes of a published 7B matrix-memory model) and delta heads of 64; "small": heads of 64 everywhere.
+NUFAPEL_SIZES = {
+    "w2k": dict(width=2048, heads=16, kv=4, dim=128, vdim=128, mem=(8, 128, 256), delta=(32, 64), rank=64, buckets=32,
+                bias_max=1024, ff=8192, experts=32, top=4, eff=1024, groups=(4, 2)),
+    "w4k": dict(width=4096, heads=32, kv=8, dim=128, vdim=128, mem=(8, 256, 512), delta=(64, 64), rank=96, buckets=32,
+                bias_max=1024, ff=16384, experts=32, top=4, eff=2048, groups=(4, 2)),
+    "small": dict(width=1024, heads=16, kv=4, dim=64, vdim=64, mem=(4, 64, 128), delta=(16, 64), rank=32, buckets=16,
+                  bias_max=256, ff=4096, experts=16, top=2, eff=1024, groups=(2, 1)),
+}
+NUFAPEL_KINDS = ("pair_dense", "delta_moe", "pair_moe")
+FP32_LANES = 148 * 128        # 32-bit multiply-adds a clock: 148 SMs of 128 lanes
+
+
+def nufapel_configs(z, layers, vocab=32000):
+    H, G = z["heads"], z["kv"]
+    mh, md, mv = z["mem"]
+    dh, dd = z["delta"]
+    pair = {"left": {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                     "bias_max": z["bias_max"], "buckets": z["buckets"]},
+            "right": {"heads": mh, "dim": md, "vdim": mv, "gate_cap": 15.0}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0,
+                      "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    three = [{"type": "parallel", "mixer": pair, "mlp": dense},
+             {"type": "general_delta", "mixer": {"heads": dh, "dim": dd, "decay_rank": z["rank"]}, "mlp": moe},
+             {"type": "parallel", "mixer": pair, "mlp": moe}]
+    nufapel = {"architecture": "Nufapel", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5},
+               "max_positions": MAX_CONTEXT + 64, "logit_softcap": 30.0,
+               "layers": [json.loads(json.dumps(three[i % 3])) for i in range(layers)]}
+    soft = {"type": "attention_2", "mlp": {"kind": "dense", "ff": z["ff"]},
+            "mixer": {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                      "rot": {"base": 5e5, "dims": z["dim"] // 2}}}
+    loselix = {"architecture": "Loselix", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+               "layers": [json.loads(json.dumps(soft)) for _ in range(layers)]}
+    return nufapel, loselix
+
+
+def nufapel_parts(model, z, layer_index, batch, tokens, reps, pk, sm_mhz):
+    """Layer `layer_index` of a Nufapel model in parts, each alone: the attention kernel, each recurrence (from the
+    projected row to the heads before the output product: prepare, scan, norm and gate), the whole mixer, the whole
+    feed-forward.  One prompt of `tokens` tokens, then one decode step of `batch` requests at CONTEXT tokens.
+    Rooflines: attention and feed-forward as for the other designs (the slower of FLOPs at the measured bf16 peak and
+    bytes at the measured copy bandwidth); a recurrence is 32-bit arithmetic on the CUDA cores by the design's rule
+    (the state and all that enters it are 32-bit), so its roofline is the slower of its multiply-adds at 148 x 128
+    lanes x the SM clock and its bytes (the state read and written once, the per-token vectors once)."""
+    import torch
+    from jax_vllm_b200 import make_driver
+    from jax_vllm_b200.engine import StepEntry
+    W = z["width"]
+    flush = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")
+    layer = model.layers[layer_index]
+    mixer, ff = layer.mixer, layer.feed_forward
+    out = {}
+    for phase in ("prefill", "decode"):
+        if phase == "prefill":
+            driver = make_driver(model, max_num_seqs=1, max_model_len=tokens + 16, block_size=PAGE, prefix_cache=False,
+                                 max_tokens_per_step=tokens, cuda_graphs=False)
+            rc = driver.cache.admit("p")
+            driver.cache.grow(rc, tokens)
+            entries = [StepEntry(rc, [(i * 7919 + 13) % 1000 for i in range(tokens)], (tokens - 1,))]
+            n, pairs, keys, seqs = tokens, tokens * (tokens + 1) // 2, tokens, 1
+        else:
+            driver = make_driver(model, max_num_seqs=batch, max_model_len=CONTEXT + 64, block_size=PAGE, prefix_cache=False,
+                                 cuda_graphs=False)
+            rcs = fake_context(driver, batch, CONTEXT)
+            for rc in rcs:
+                driver.cache.grow(rc, rc.num_tokens + 1)
+            entries = [StepEntry(rc, [b], (0,)) for b, rc in enumerate(rcs)]
+            n, pairs, keys, seqs = batch, batch * (CONTEXT + 1), batch * (CONTEXT + 1), batch
+        step = driver.runner.builder.build(entries)
+        cache = driver.runner.layer_caches[layer_index]
+        x = (torch.randn((n, W), device="cuda") * 0.5).to(torch.bfloat16)
+        jobs = []
+
+        def recurrence(part, view, removal):
+            row = (torch.randn((n, part.in_rows), device="cuda") * 0.5).to(torch.bfloat16)
+            heads = torch.empty((n, part.heads_out), dtype=torch.bfloat16, device="cuda")
+            d = part.d
+            v = part.heads_out // part.h
+            fma = n * part.h * d * v * (4 if removal else 3)                  # decay, write, read (and remove: +1 dot, +1 update)
+            nbytes = seqs * 2 * part.h * d * v * 4 + n * part.in_rows * 2 + n * part.heads_out * 2
+            t_fma, t_bytes = fma / (FP32_LANES * sm_mhz * 1e6) * 1e6, nbytes / (pk["hbm_gbs"] * 1e9) * 1e6
+            return (lambda: part.from_projection(row, step, view, heads)), (t_fma, t_bytes, "fp32 lanes")
+
+        if hasattr(mixer, "sides"):
+            att, mem = mixer.sides
+            q = torch.randn((n, att.hq * att.d), device="cuda").to(torch.bfloat16)
+            a = torch.empty((n, att.hq * att.dv), dtype=torch.bfloat16, device="cuda")
+            table = step.block_tables[cache[0].group]
+            flops = 2 * att.hq * (att.d + att.dv) * pairs
+            nbytes = keys * (att.hk * att.d + att.hv * att.dv) * 2 + n * att.hq * (att.d + att.dv) * 2
+            jobs.append(("attention kernel", lambda: att.attend(q, a, step, cache[0], table),
+                         (flops / (pk["bf16_tflops"] * 1e12) * 1e6, nbytes / (pk["hbm_gbs"] * 1e9) * 1e6, "flops")))
+            jobs.append(("memory recurrence",) + recurrence(mem, cache[1], False))
+        else:
+            jobs.append(("delta recurrence",) + recurrence(mixer, cache, True))
+        jobs.append(("mixer", lambda: mixer.forward(x, step, cache), None))
+        if ff is not None:
+            if layer_index % 3 != 0:                                          # routed experts
+                hit = z["experts"] * (1 - (1 - z["top"] / z["experts"]) ** n)
+                ff_flops, ff_bytes = 2 * n * z["top"] * 3 * z["eff"] * W, hit * 3 * z["eff"] * W * 2
+            else:
+                ff_flops, ff_bytes = 2 * n * 2 * z["ff"] * W, 2 * z["ff"] * W * 2
+            jobs.append(("feed-forward", lambda: ff.forward(x, step),
+                         (ff_flops / (pk["bf16_tflops"] * 1e12) * 1e6, ff_bytes / (pk["hbm_gbs"] * 1e9) * 1e6, "flops")))
+        res = {}
+        for name, fn, roof in jobs:
+            us = time_part(fn, reps, flush)
+            res[name] = {"us": round(us, 1)}
+            if roof is not None:
+                t_math, t_bytes, unit = roof
+                ideal = max(t_math, t_bytes)
+                res[name].update(roofline_us=round(ideal, 1), bound=unit if t_math >= t_bytes else "bytes",
+                                 of_roofline=round(ideal / us, 3))
+        driver.runner.check_kernels()
+        out[phase] = res
+        del driver
+        torch.cuda.empty_cache()
+    return out
+
+
+def design_nufapel(layers, sizes, steps, warmup) -> int:
+    import torch
+    from jax_vllm_b200 import random_model, registry
+    pk, pk_src = peaks()
+    sizes = [t for t in sizes if t in NUFAPEL_SIZES] or ["w2k", "w4k"]
+    out = {"design": "nufapel", "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_batch": 8, "context": CONTEXT,
+           "dtype": "bf16", "data": "synthetic (random weights, seed 5)", "peaks": pk, "peak_source": pk_src, "sizes": {}}
+    for tag in sizes:
+        z = NUFAPEL_SIZES[tag]
+        n_cfg, l_cfg = nufapel_configs(z, layers)
+        row = {"nufapel": {"config": {k: v for k, v in z.items()}},
+               "loselix": {"config": {"width": z["width"], "heads": z["heads"], "kv": z["kv"], "dim": z["dim"], "ff": z["ff"]}}}
+        for kind, cfg in (("nufapel", n_cfg), ("loselix", l_cfg)):
+            model = random_model(registry.config_from_dict(cfg), seed=5, dtype="bf16", device="cuda:0")
+            with ClockSampler() as clocks:
+                pms = time_prefill(model, PREFILL_TOKENS, warmup=2, reps=5)
+                dms, launches, _, _ = time_decode(model, 8, steps, warmup)
+            row[kind].update(prefill_tok_s=round(PREFILL_TOKENS / (pms / 1e3), 1), prefill_ms=round(pms, 3),
+                             decode_tok_s=round(8 / (dms / 1e3), 1), decode_ms_per_step=round(dms, 4),
+                             decode_launches_per_step=launches, clocks=clocks.summary)
+            if kind == "loselix":
+                lz = dict(z, soft=(z["dim"], z["vdim"], z["dim"] // 2))
+                row[kind]["parts"] = design_parts(model, kind, lz, 0, 8, PREFILL_TOKENS, 7, pk)
+            else:
+                mhz = float(clocks.summary.get("sm_max_mhz") or 1965.0)
+                row[kind]["fp32_peak_tflops"] = round(2 * FP32_LANES * mhz * 1e6 / 1e12, 1)
+                row[kind]["parts"] = {NUFAPEL_KINDS[i]: nufapel_parts(model, z, i, 8, PREFILL_TOKENS, 7, pk, mhz)
+                                      for i in range(min(3, layers))}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][tag] = row
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm():
     why = ("the reference (jllm) needs jax, jaxlib and equinox and the hatchling build backend; none is installed "
            "and none is in the offline wheelhouse, so it can neither be installed nor run here")
@@ -778,11 +942,12 @@ def main():
     ap.add_argument("--with-workloads", action="store_true",
                     help="after the headline run, also run the two serving workloads and add their lines under `workloads`")
     ap.add_argument("--design", default=None, metavar="NAME",
-                    help="guronex or loselix: that design's prefill and decode throughput at a few layer sizes beside "
-                         "Qwen3 of equal size, with the rooflines of its attention and feed-forward (see design())")
+                    help="guronex, loselix or nufapel: that design's prefill and decode throughput at a few layer sizes "
+                         "beside its closest neighbour of equal size (Qwen3; for nufapel, Loselix), with the rooflines of "
+                         "its kernels (see design())")
     ap.add_argument("--sizes", default="lite,mid,row576",
                     help="with --design: which of its layer sizes, comma-separated (guronex: lite,mid,row576; loselix: "
-                         "w2k,w4k,mix, all by default)")
+                         "w2k,w4k,mix, all by default; nufapel: w2k,w4k,small, the first two by default)")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()

@@ -7,6 +7,9 @@
 //   score cap      s <- cap * tanh(s / cap) on the scaled score
 //   sigmoid        the weight of a visible key is sigmoid(s + bias[query head]); no maximum, no sum, no division
 //   float output   two score maps are subtracted by the caller in 32-bit
+//   head scale     the scaled score of query head h is multiplied by head_scale[h] (a temperature per head)
+//   distance bias  dist_bias[h][min(pos - j, n_dist - 1)] is added to the score of key j; no scale touches it
+//   sink           exp(sink[h]) counts once in the softmax's denominator; it has no key and no value
 //
 // Scores are scaled and masked in 32-bit, the running softmax keeps (max, sum) in 32-bit, weights are rounded to
 // bfloat16 for the second product.  Tiles, the split of a decoded token's keys and the merge by the block that ends
@@ -46,6 +49,10 @@ struct Params {
   float score_cap;             // > 0: s <- cap * tanh(s / cap)
   int sigmoid;                 // independent weights sigmoid(s + bias[query head])
   const float* bias;           // [n_q_heads] or null
+  const float* head_scale;     // [n_q_heads] or null
+  const float* dist_bias;      // [n_q_heads][n_dist] or null: row h serves head h, column = how far back the key lies
+  int n_dist;                  //   (distances of n_dist - 1 and more share the last column)
+  const float* sink;           // [n_q_heads] or null (softmax only)
   int out_f32;                 // `out` is float
   int n_v_heads;
   int tokens_per_tile, heads_per_tile, n_head_groups, split_size, n_splits;
@@ -198,14 +205,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // lane/4 + 8, -1 for an unused row); tiles that lie wholly inside every row's visible range go without it.
 template <int NB, bool MASK>
 __device__ __forceinline__ void weights_tile(float (&s)[NB][4], float (&o)[VD / 8][4], float (&m)[2], float (&l)[2],
-                                             int pos0, int pos1, int key0, int j_end, int window, float scale,
+                                             int pos0, int pos1, int key0, int j_end, int window, float scale0,
+                                             float scale1, const float* dist0, const float* dist1, int n_dist,
                                              float cap, bool sigmoid, float bias0, float bias1, int lane) {
   const float cap_exp = cap > 0.f ? 2.f * LOG2E / cap : 0.f;
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float v = s[nb][i] * scale;
+      float v = s[nb][i] * ((i < 2) ? scale0 : scale1);
+      if (dist0 != nullptr) {     // by how far back the key lies; rows without a position and hidden keys read column 0
+        const int back = ((i < 2) ? pos0 : pos1) - (key0 + nb * 8 + (lane & 3) * 2 + (i & 1));
+        v += __ldg(((i < 2) ? dist0 : dist1) + min(max(back, 0), n_dist - 1));
+      }
       // tanh(x) = 1 - 2 / (1 + e^(2x)): one ex2 and one reciprocal; its absolute error (about 1e-7) times the cap is
       // far below what the 16-bit operands of the product leave in a score
       if (cap > 0.f) v = fmaf(-2.f * cap, fast_rcp(1.f + fast_exp2(v * cap_exp)), cap);
@@ -322,7 +334,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_general_kernel(const Par
   __syncthreads();                        // rows[0] has been read by all before iteration 0 refills it
 
   // ---- this thread's two rows
-  int pos[2];
+  int pos[2], row_head[2];
   float bias[2] = {0.f, 0.f};
   {
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
@@ -333,6 +345,15 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_general_kernel(const Par
       if (h0 < G) bias[0] = p.bias[kv_head * G + h0];
       if (h1 < G) bias[1] = p.bias[kv_head * G + h1];
     }
+    row_head[0] = kv_head * G + min(h0, G - 1);
+    row_head[1] = kv_head * G + min(h1, G - 1);
+  }
+  float scale[2] = {p.scale, p.scale};
+  const float* dist[2] = {nullptr, nullptr};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (p.head_scale != nullptr) scale[h] *= p.head_scale[row_head[h]];
+    if (p.dist_bias != nullptr) dist[h] = p.dist_bias + (size_t)row_head[h] * p.n_dist;
   }
   const bool sigmoid = p.sigmoid != 0;
   // the last position any row of this warp has (its tiles beyond that are skipped)
@@ -374,10 +395,10 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_general_kernel(const Par
       // the test is needed only where the tile reaches past the first row's position, past the end,
       // or a window cuts into it
       if (key0 + BN - 1 > warp_first || key0 + BN > j_hi || p.window > 0)
-        weights_tile<BN / 8, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale, p.score_cap, sigmoid,
+        weights_tile<BN / 8, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, scale[0], scale[1], dist[0], dist[1], p.n_dist, p.score_cap, sigmoid,
                                    bias[0], bias[1], lane);
       else
-        weights_tile<BN / 8, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale, p.score_cap, sigmoid,
+        weights_tile<BN / 8, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, scale[0], scale[1], dist[0], dist[1], p.n_dist, p.score_cap, sigmoid,
                                     bias[0], bias[1], lane);
       pv_tile<VD, BN / 8>(o_acc, s, vs + buf * BN * SV, lane);
     }
@@ -396,7 +417,12 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_general_kernel(const Par
     const int r = warp * 16 + (lane >> 2) + h * 8;
     const int t = r / HPT, hh = hg * HPT + r % HPT;
     const size_t at = (size_t)(q_begin + q_off + t) * p.out_stride + (size_t)(kv_head * G + hh) * VD;
-    const float inv = sigmoid ? 1.f : 1.f / l[h];
+    float inv = sigmoid ? 1.f : 1.f / l[h];
+    if (p.sink != nullptr) {     // the sink joins the denominator, both brought to the larger of the two maxima
+      const float sk = p.sink[row_head[h]], mx = fmaxf(m[h], sk);
+      const float e = __expf(m[h] - mx);
+      inv = e / (l[h] * e + __expf(sk - mx));
+    }
 #pragma unroll
     for (int db = 0; db < VD / 8; ++db) {
       const int d = db * 8 + (lane & 3) * 2;
@@ -457,7 +483,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_general_kernel(const Para
   __syncthreads();                        // rows[0] has been read by all before iteration 0 refills it
 
   // every row is the same token: position pos_q for rows that hold a head, -1 otherwise
-  int pos[2];
+  int pos[2], row_head[2];
   float bias[2] = {0.f, 0.f};
   {
     const int r0 = lane >> 2, r1 = r0 + 8;
@@ -467,6 +493,15 @@ __global__ void __launch_bounds__(THREADS) attn_decode_general_kernel(const Para
       if (pos[0] >= 0) bias[0] = p.bias[kv_head * G + hg * HPT + r0];
       if (pos[1] >= 0) bias[1] = p.bias[kv_head * G + hg * HPT + r1];
     }
+    row_head[0] = kv_head * G + min(hg * HPT + r0, G - 1);
+    row_head[1] = kv_head * G + min(hg * HPT + r1, G - 1);
+  }
+  float scale[2] = {p.scale, p.scale};
+  const float* dist[2] = {nullptr, nullptr};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (p.head_scale != nullptr) scale[h] *= p.head_scale[row_head[h]];
+    if (p.dist_bias != nullptr) dist[h] = p.dist_bias + (size_t)row_head[h] * p.n_dist;
   }
   const bool sigmoid = p.sigmoid != 0;
   float o_acc[VD / 8][4];
@@ -502,9 +537,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_general_kernel(const Para
       qk_tile<KD, 2>(s, qs, ks + (buf * BN + warp * 16) * SK, lane);
       // keys before j_lo are never loaded, so only the tile that reaches past j_hi needs the test
       if (key0 + 16 > j_hi)
-        weights_tile<2, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, 0, p.scale, p.score_cap, sigmoid, bias[0], bias[1], lane);
+        weights_tile<2, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, 0, scale[0], scale[1], dist[0], dist[1], p.n_dist, p.score_cap, sigmoid, bias[0], bias[1], lane);
       else
-        weights_tile<2, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, 0, p.scale, p.score_cap, sigmoid, bias[0], bias[1], lane);
+        weights_tile<2, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, 0, scale[0], scale[1], dist[0], dist[1], p.n_dist, p.score_cap, sigmoid, bias[0], bias[1], lane);
       pv_tile<VD, 2>(o_acc, s, vs + (buf * BN + warp * 16) * SV, lane);
     }
     __syncthreads();
@@ -580,9 +615,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_general_kernel(const Para
     if (hh >= G) continue;
     const int head = kv_head * G + hh;
     const size_t base = ((size_t)blockIdx.x * p.n_q_heads + head) * p.n_splits;
-    float m_all = -INFINITY;
+    // the sink is one more part, with no value: maximum sink, sum 1 (maxima are exponents of two here)
+    const float sk = p.sink != nullptr ? p.sink[head] * LOG2E : -INFINITY;
+    float m_all = sk;
     for (int sp = s_first; sp <= s_last; ++sp) m_all = fmaxf(m_all, __ldcg(p.part_ml + (base + sp) * 2));
-    float o = 0.f, l_all = 0.f;
+    float o = 0.f, l_all = p.sink != nullptr ? exp2f(sk - m_all) : 0.f;
     for (int sp = s_first; sp <= s_last; ++sp) {
       const float f = exp2f(__ldcg(p.part_ml + (base + sp) * 2) - m_all);
       l_all += f * __ldcg(p.part_ml + (base + sp) * 2 + 1);
@@ -646,9 +683,11 @@ JV_EXPORT int jv_attn_general_mma(const void* q, int q_stride, void* out, int ou
                                   const int* block_table, int table_width, const int* cu_seqlens, const int* start_pos,
                                   const int* work, int n_work, int n_q_heads, int n_kv_heads, int n_v_heads, int key_dim,
                                   int value_dim, int page_size, int num_pages, int window, float scale, float score_cap,
-                                  int sigmoid, const float* bias, int split_size, int n_splits, int* status,
+                                  int sigmoid, const float* bias, const float* head_scale, const float* dist_bias,
+                                  int n_dist, const float* sink, int split_size, int n_splits, int* status,
                                   cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
+  if ((dist_bias != nullptr && n_dist < 1) || (sink != nullptr && sigmoid)) return JV_ERR_UNSUPPORTED;
   if (key_dim != KD || value_dim != VD || n_kv_heads < 1 || n_v_heads < 1 || n_q_heads % n_kv_heads != 0)
     return JV_ERR_UNSUPPORTED;
   if ((q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) || ((uintptr_t)out % 8) || ((uintptr_t)k_cache % 16) ||
@@ -663,6 +702,7 @@ JV_EXPORT int jv_attn_general_mma(const void* q, int q_stride, void* out, int ou
   p.work = work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.n_v_heads = n_v_heads; p.page_size = page_size;
   p.num_pages = num_pages; p.window = window; p.scale = scale; p.score_cap = score_cap; p.sigmoid = sigmoid ? 1 : 0;
   p.bias = bias; p.status = status;
+  p.head_scale = head_scale; p.dist_bias = dist_bias; p.n_dist = n_dist; p.sink = sink;
   const int G = n_q_heads / n_kv_heads;
   p.heads_per_tile = G < 16 ? G : 16;
   p.n_head_groups = (G + p.heads_per_tile - 1) / p.heads_per_tile;

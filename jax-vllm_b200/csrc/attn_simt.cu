@@ -40,7 +40,7 @@ struct AttnParams {
   const float* bias;         // [n_q_heads] or null
   int out_f32;               // 1: `out` is float whatever the type of q and the cache
   const float* head_scale;   // [n_q_heads] or null: multiplies the scaled score of its head (a temperature per head)
-  const float* dist_bias;    // [n_dist][n_q_heads] or null: added to the score of a key `pos - j` positions back; distances
+  const float* dist_bias;    // [n_q_heads][n_dist] or null: added to the score of a key `pos - j` positions back; distances
   int n_dist;                //   of n_dist - 1 and more share the last row.  Neither `scale` nor `head_scale` touch it.
   const float* sink;         // [n_q_heads] or null (softmax): exp(sink) counts once in the denominator, with no value
   int* status;
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
         if (p.head_scale != nullptr || p.dist_bias != nullptr) {
           const int hq = min(hg * p.heads_per_tile + m % p.heads_per_tile, G - 1) + kv_head * G;
           if (p.head_scale != nullptr) sc *= p.head_scale[hq];
-          if (p.dist_bias != nullptr && vis) sc += p.dist_bias[(size_t)min(pos - j, p.n_dist - 1) * p.n_q_heads + hq];
+          if (p.dist_bias != nullptr && vis) sc += p.dist_bias[(size_t)hq * p.n_dist + min(pos - j, p.n_dist - 1)];
         }
         if (p.score_cap > 0.f) sc = p.score_cap * tanhf(sc / p.score_cap);
         if (p.sigmoid) {

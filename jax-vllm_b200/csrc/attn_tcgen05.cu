@@ -53,6 +53,9 @@ struct Params {
   float scale_log2;
   int sigmoid;                 // 1: the weight of a visible key is sigmoid(score * scale + bias[query head]): no maximum,
   const float* bias;           //    no sum, no division ([n_q_heads] floats or null)
+  // softmax only: the scaled score of head h is multiplied by head_scale[h]; dist_bias[h][min(pos - j, n_dist - 1)] is
+  // added to the score of key j (untouched by the scales); exp(sink[h]) counts once in the denominator.  Each may be null.
+  const float* head_scale; const float* dist_bias; int n_dist; const float* sink;
   int* status;
 };
 
@@ -456,6 +459,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       const int pos = row_ok ? pos_first + t : -1;
       // sigmoid weights: the bias of this row's head, in the exponent's unit
       const float bias_log2 = (p.sigmoid && p.bias != nullptr && row_ok) ? p.bias[it.kv_head * G + hh] * LOG2E : 0.f;
+      // With a head's own scale or a bias by distance the scores are first brought to the exponent's unit, s * scale *
+      // head_scale * log2(e) + bias * log2(e), and the maximum, the reference and the exponentials work on that (`sc`,
+      // what still multiplies a score in the exponent, is then 1).  The same for every thread of the block.
+      const bool shaped = p.head_scale != nullptr || p.dist_bias != nullptr;
+      const int head = it.kv_head * G + min(hh, G - 1);
+      const float sc = shaped ? 1.f : p.scale_log2;
+      const float row_scale = p.scale_log2 * (p.head_scale != nullptr ? p.head_scale[head] : 1.f);
+      const float* dist_row = p.dist_bias != nullptr ? p.dist_bias + (size_t)head * p.n_dist : nullptr;
       // m_ref is the reference maximum that the exponentials are taken against.  It follows the true
       // maximum lazily: only when the maximum has grown by more than 2^8 (in the exponent) is O rescaled,
       // which is rare after the first tiles; until then probabilities may exceed 1 by at most that factor.
@@ -475,6 +486,18 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           tmem_ld32_issue(s_addr, sr[0]);
           tmem_ld32_issue(s_addr + 32, sr[1]);
           tmem_ld_wait();
+          if (shaped) {
+            const int back0 = pos - key0;                        // how far back this thread's first key lies
+            const int last_col = p.n_dist - 1;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float v = __uint_as_float(sr[c][i]) * row_scale;
+                if (dist_row != nullptr) v = fmaf(__ldg(dist_row + min(max(back0 - (c * 32 + i), 0), last_col)), LOG2E, v);
+                sr[c][i] = __float_as_uint(v);
+              }
+          }
           // masking is a loop of its own behind a branch that the whole block takes or not: only the last
           // tile of an item has keys to hide
           if (need_mask) {
@@ -497,19 +520,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         // with keys, rarely later): one barrier tells all 256 threads whether any row is in that case, and only
         // then do the two threads of a row exchange their maxima
         const bool outgrown = !p.sigmoid && ok && my_max != -INFINITY &&
-                              (m_ref == -INFINITY || (my_max - m_ref) * p.scale_log2 > LAZY);
+                              (m_ref == -INFINITY || (my_max - m_ref) * sc > LAZY);
         float alpha = 1.f;
         if (pair_barrier_or(quad, outgrown)) {
           sh->xch[half][row] = my_max;
           pair_barrier(quad);
           const float m_tile = fmaxf(sh->xch[0][row], sh->xch[1][row]);
           pair_barrier(quad);                                        // both have read before a later tile writes
-          if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > LAZY)) {
-            alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * p.scale_log2);
+          if (ok && m_tile != -INFINITY && (m_ref == -INFINITY || (m_tile - m_ref) * sc > LAZY)) {
+            alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_tile) * sc);
             m_ref = m_tile;
           }
         }
-        const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * p.scale_log2;
+        const float m_scaled = (m_ref == -INFINITY) ? 0.f : m_ref * sc;
         // ---- O is rescaled only if some row of this warp moved its reference; the previous P V must be complete then
         if (ok && j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
           ok = __all_sync(0xffffffffu, mbar_wait(&sh->o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1));
@@ -546,7 +569,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
             }
           tmem_st32_bits(tmem + lane_addr + TMEM_P + (gt & 1) * 64 + half * 32, pw);
         } else {
-          const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_scaled, -m_scaled);
+          const uint64_t scale2 = pack2(sc, sc), neg_m2 = pack2(-m_scaled, -m_scaled);
           uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
           uint32_t pw[32];
 #pragma unroll
@@ -597,7 +620,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       const float l_row = sh->xch[0][row] + sh->xch[1][row];
       pair_barrier(quad);                                        // both have read before the next item's first tile writes
       const bool got = ok && mbar_wait(&sh->o_done[g_last & 1], (g_last >> 1) & 1);
-      const float inv = row_ok ? (p.sigmoid ? 1.f : 1.f / l_row) : 0.f;
+      float inv = row_ok ? (p.sigmoid ? 1.f : 1.f / l_row) : 0.f;
+      if (p.sink != nullptr && row_ok && m_ref != -INFINITY) {
+        // the sink joins the denominator: the row's sum stands against the reference m_ref * sc (an exponent of two)
+        const float sk = p.sink[head] * LOG2E, mr = m_ref * sc, mx = fmaxf(mr, sk);
+        const float e = fast_exp2(mr - mx);
+        inv = e / (l_row * e + fast_exp2(sk - mx));
+      }
       const bool whole = it.tokens_here == p.tokens_per_tile;
       // A whole tile leaves through shared memory (where the item's queries were: every product with them has
       // completed) and one TMA store per half of the head; threads that write their 128 bytes to rows 8 KB apart in
@@ -702,12 +731,16 @@ JV_EXPORT int jv_attn_tcgen05_tokens_per_tile(int n_q_heads, int n_kv_heads) { r
 // k_cache/v_cache: [num_pages, page_size, n_kv_heads, 128]; work: [n_work, 2] (entry, first token of the tile),
 // tiles of jv_attn_tcgen05_tokens_per_tile tokens, in ascending order of work.
 // sigmoid != 0: the weights are sigmoid(q.k * scale + bias[query head]) instead of a softmax (bias: [n_q_heads] floats or null).
+// head_scale [n_q_heads], dist_bias [n_q_heads][n_dist], sink [n_q_heads] (floats, each may be null; softmax only): see Params.
 JV_EXPORT int jv_attn_tcgen05_ex(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
                                  const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,
                                  const int* start_pos, const int* work, int n_work, int n_q_heads, int n_kv_heads,
                                  int head_dim, int page_size, int num_pages, float scale, int sigmoid, const float* bias,
+                                 const float* head_scale, const float* dist_bias, int n_dist, const float* sink,
                                  int* status, cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
+  if ((dist_bias != nullptr && n_dist < 1) || (sigmoid && (head_scale != nullptr || dist_bias != nullptr || sink != nullptr)))
+    return JV_ERR_UNSUPPORTED;
   if (!jv_attn_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size, 0)) return JV_ERR_UNSUPPORTED;
   if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_cache % 16) ||
       ((uintptr_t)v_cache % 16))
@@ -743,6 +776,7 @@ JV_EXPORT int jv_attn_tcgen05_ex(const void* q, int q_stride, int n_tokens, void
   p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_work = n_work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
   p.scale_log2 = scale * LOG2E; p.status = status; p.sigmoid = sigmoid ? 1 : 0; p.bias = bias;
+  p.head_scale = head_scale; p.dist_bias = dist_bias; p.n_dist = n_dist; p.sink = sink;
   constexpr size_t smem = TILE_BYTES * (Q_BUFFERS + K_STAGES + V_STAGES) + sizeof(Shared) + 1024;
   static bool ready[JV_MAX_DEVICES];
   if (!jv_once_per_device(ready, [&] {
@@ -767,5 +801,5 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
                               int head_dim, int page_size, int num_pages, float scale, int* status, cudaStream_t stream) {
   return jv_attn_tcgen05_ex(q, q_stride, n_tokens, out, out_stride, k_cache, v_cache, block_table, table_width, cu_seqlens,
                             start_pos, work, n_work, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, scale, 0, nullptr,
-                            status, stream);
+                            nullptr, nullptr, 0, nullptr, status, stream);
 }

@@ -15,9 +15,11 @@
 //                            i = cap tanh((z_i + i0) / cap), f = logsigmoid(cap tanh((z_f + f0) / cap)),
 //                            m' = max(f + m, i), keep = exp(f + m - m'), take = exp(i - m'),
 //                            n <- keep n + take k, den = max(|n . q|, exp(-m')) + 1e-6,
-//                            w = keep (every channel), k <- take k, r = q / den, no removal term
-//                                                                                   (jv_memory_gates, a scan of its own
-//                                                                                   over n and m, one warp a head)
+//                            w = keep (every channel), k <- take k, r = q, no removal term; n is one more column
+//                            of the state whose value is 1, so n . q is that column's output, and o is divided by
+//                            den when the heads are normed          (jv_memory_gates: a scan over m alone, one warp a
+//                                                                    head, an add and a max a token; then all tokens
+//                                                                    at once)
 //
 // The columns of S evolve independently of one another, so the scan is parallel over (entry, head, value column) and
 // serial over an entry's tokens: a warp holds 8 columns x 4 lanes that share the key channels; a thread keeps its
@@ -72,17 +74,17 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// One warp per (entry, head): the scan over the normaliser n [D] and the running maximum m.  packed: [n, heads, 3, D]
-// (r, k, w).  state_n: [slots][heads * D] and state_m: [slots][heads], rows `slot_stride` floats apart.
-constexpr int GATE_NPT = 8;     // key channels per lane: key sizes up to 256
+// The gates of the matrix memory in two kernels.  (1) One warp per (entry, head) scans the running maximum: the two
+// log gates of 32 tokens are formed side by side, one per lane, then the chain m' = max(f + m, i), which is all that
+// is serial, runs over the lanes in order (an add and a max a token).  gates: [n, heads, 4] = (keep, take, m', -);
+// the fourth place receives n . q from the scan.  state_m: [slots][heads], rows `slot_stride` floats apart.
 template <typename T, typename W>
-__global__ void __launch_bounds__(32) memory_gates_kernel(const T* __restrict__ proj, long long stride, int q_off, int k_off,
-                                                          int i_off, int f_off, const W* __restrict__ i_bias,
-                                                          const W* __restrict__ f_bias, float cap, float q_scale,
-                                                          float* __restrict__ packed, float* __restrict__ state_n,
-                                                          float* __restrict__ state_m, long long slot_stride,
-                                                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                                                          int n_slots, int heads, int D, int* __restrict__ status) {
+__global__ void __launch_bounds__(32) gate_scan_kernel(const T* __restrict__ proj, long long stride, int i_off, int f_off,
+                                                       const W* __restrict__ i_bias, const W* __restrict__ f_bias,
+                                                       float cap, float* __restrict__ gates, float* __restrict__ state_m,
+                                                       long long slot_stride, const int* __restrict__ cu_seqlens,
+                                                       const int* __restrict__ slots, int n_slots, int heads,
+                                                       int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   const int entry = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
@@ -92,67 +94,59 @@ __global__ void __launch_bounds__(32) memory_gates_kernel(const T* __restrict__ 
     if (lane == 0) atomicOr(status, JV_STATUS_BAD_ROW);
     return;
   }
-  float* sn = state_n + (size_t)slot * slot_stride + (size_t)h * D;
   float* sm = state_m + (size_t)slot * slot_stride + h;
-  float nv[GATE_NPT], q[GATE_NPT], k[GATE_NPT], qn[GATE_NPT], kn[GATE_NPT];
-#pragma unroll
-  for (int i = 0; i < GATE_NPT; ++i) {
-    const int d = lane + 32 * i;
-    nv[i] = d < D ? sn[d] : 0.f;
-    qn[i] = kn[i] = 0.f;
-  }
   float m = *sm;
   const float ib = to_f32(i_bias[h]), fb = to_f32(f_bias[h]);
-  float zi_n = 0.f, zf_n = 0.f;
-  auto fetch = [&](int t) {
-    const T* row = proj + (size_t)t * stride;
-#pragma unroll
-    for (int i = 0; i < GATE_NPT; ++i) {
-      const int d = lane + 32 * i;
-      if (d < D) {
-        qn[i] = to_f32(row[q_off + h * D + d]);
-        kn[i] = to_f32(row[k_off + h * D + d]);
-      }
+  auto fetch = [&](int t, float& zi, float& zf) {
+    if (t < t1) {
+      const T* row = proj + (size_t)t * stride;
+      zi = to_f32(row[i_off + h]);
+      zf = to_f32(row[f_off + h]);
     }
-    zi_n = to_f32(row[i_off + h]);
-    zf_n = to_f32(row[f_off + h]);
   };
-  if (t0 < t1) fetch(t0);
-  for (int t = t0; t < t1; ++t) {
-#pragma unroll
-    for (int i = 0; i < GATE_NPT; ++i) { q[i] = qn[i]; k[i] = kn[i]; }
+  float zi_n = 0.f, zf_n = 0.f;
+  fetch(t0 + lane, zi_n, zf_n);
+  for (int base = t0; base < t1; base += 32) {
+    const int t = base + lane;
     const float zi = zi_n, zf = zf_n;
-    if (t + 1 < t1) fetch(t + 1);                       // the next token's loads fly while this one is computed
-    const float gi = cap * tanhf((zi + ib) / cap);
-    const float gf = log_sigmoid(cap * tanhf((zf + fb) / cap));
-    const float m_new = fmaxf(gf + m, gi);
-    const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
-    m = m_new;
-    float dot = 0.f;
+    fetch(t + 32, zi_n, zf_n);                          // the next group's loads fly while this one is computed
+    // a lane without a token leaves the maximum as it is: f = 0, i = -inf
+    const float gi = t < t1 ? cap * tanhf((zi + ib) / cap) : -INFINITY;
+    const float gf = t < t1 ? log_sigmoid(cap * tanhf((zf + fb) / cap)) : 0.f;
+    float before = 0.f, after = 0.f;
 #pragma unroll
-    for (int i = 0; i < GATE_NPT; ++i) {
-      nv[i] = fmaf(keep, nv[i], take * k[i]);
-      dot = fmaf(nv[i], q[i] * q_scale, dot);
+    for (int l = 0; l < 32; ++l) {
+      const float f = __shfl_sync(0xffffffffu, gf, l), i = __shfl_sync(0xffffffffu, gi, l);
+      const float m_new = fmaxf(f + m, i);
+      if (lane == l) { before = m; after = m_new; }
+      m = m_new;
     }
-    dot = warp_sum(dot);
-    const float inv = 1.f / (fmaxf(fabsf(dot), expf(-m)) + 1e-6f);
-    float* out = packed + ((size_t)t * heads + h) * 3 * D;
-#pragma unroll
-    for (int i = 0; i < GATE_NPT; ++i) {
-      const int d = lane + 32 * i;
-      if (d < D) {
-        out[d] = q[i] * q_scale * inv;
-        out[D + d] = take * k[i];
-        out[2 * D + d] = keep;
-      }
+    if (t < t1) {
+      float* out = gates + ((size_t)t * heads + h) * 4;
+      out[0] = expf(gf + before - after);
+      out[1] = expf(gi - after);
+      out[2] = after;
     }
-  }
-#pragma unroll
-  for (int i = 0; i < GATE_NPT; ++i) {
-    const int d = lane + 32 * i;
-    if (d < D) sn[d] = nv[i];
   }
   if (lane == 0) *sm = m;
+}
+
+// (2) Per token and head, all at once: packed [n, heads, 3, D] = (q * q_scale, take * k, keep in every channel).
+template <typename T>
+__global__ void __launch_bounds__(128) memory_prepare_kernel(const T* __restrict__ proj, long long stride, int q_off,
+                                                             int k_off, float q_scale, const float* __restrict__ gates,
+                                                             float* __restrict__ packed, int heads, int D) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x, h = blockIdx.y;
+  const T* row = proj + (size_t)n * stride;
+  const float keep = gates[((size_t)n * heads + h) * 4], take = gates[((size_t)n * heads + h) * 4 + 1];
+  float* out = packed + ((size_t)n * heads + h) * 3 * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    out[d] = to_f32(row[q_off + h * D + d]) * q_scale;
+    out[D + d] = take * to_f32(row[k_off + h * D + d]);
+    out[2 * D + d] = keep;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------- scan
@@ -163,6 +157,9 @@ struct ScanParams {
   float* state; long long slot_stride;               // S of (slot, head) at state + slot * slot_stride + head * D * V
   const int* cu_seqlens; const int* slots;
   int n_slots, heads, D, V;
+  // one more column, number V, with the value 1 for every token (the normaliser of a matrix memory): its state is
+  // state_n [slots][heads * D] (rows `slot_stride` apart) and its output goes to nq[(token * heads + head) * nq_stride]
+  float* state_n; float* nq; int nq_stride;
   int* status;
 };
 
@@ -200,18 +197,22 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
     return;
   }
   if (t0 >= t1) return;
-  const bool live = col < V;
-  float* S_g = p.state + (size_t)slot * p.slot_stride + (size_t)h * D * V;
+  const bool is_n = !REMOVAL && p.state_n != nullptr && col == V;
+  const bool live = col < V || is_n;
+  // element kk of this thread's column: S_g[kk * S_step]
+  float* S_g = is_n ? p.state_n + (size_t)slot * p.slot_stride + (size_t)h * D
+                    : p.state + (size_t)slot * p.slot_stride + (size_t)h * D * V + col;
+  const size_t S_step = is_n ? 1 : V;
   float S[KPT];
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kl * KPT + i;
-    S[i] = (live && kk < D) ? S_g[(size_t)kk * V + col] : 0.f;
+    S[i] = (live && kk < D) ? S_g[(size_t)kk * S_step] : 0.f;
   }
   for (int i = tid; i < 2 * CHUNK * NV * ROW; i += SCAN_THREADS) smem[i] = 0.f;     // the padding stays zero
   __syncthreads();
 
-  const T* vsrc = (const T*)p.v + p.v_off + (size_t)h * V + (live ? col : 0);
+  const T* vsrc = (const T*)p.v + p.v_off + (size_t)h * V + (col < V ? col : 0);
   auto stage = [&](int buf, int first) {
     // vectors of tokens first .. first + CHUNK - 1 (those that exist) into buffer `buf`
     const int tokens = min(CHUNK, t1 - first);
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
   auto fetch_v = [&](float* dst, int first) {
 #pragma unroll
     for (int t = 0; t < CHUNK; ++t)
-      dst[t] = (first + t < t1) ? to_f32(vsrc[(size_t)(first + t) * p.v_stride]) : 0.f;
+      dst[t] = is_n ? 1.f : (first + t < t1) ? to_f32(vsrc[(size_t)(first + t) * p.v_stride]) : 0.f;
   };
   stage(0, t0);
   fetch_v(vr, t0);
@@ -272,7 +273,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
       }
       o += __shfl_xor_sync(0xffffffffu, o, 8);
       o += __shfl_xor_sync(0xffffffffu, o, 16);
-      if (kl == 0 && live) p.out[(size_t)(first + t) * p.heads * V + (size_t)h * V + col] = o;
+      if (kl == 0 && live) {
+        if (is_n) p.nq[((size_t)(first + t) * p.heads + h) * p.nq_stride] = o;
+        else p.out[(size_t)(first + t) * p.heads * V + (size_t)h * V + col] = o;
+      }
     }
 #pragma unroll
     for (int t = 0; t < CHUNK; ++t) vr[t] = vn[t];
@@ -280,7 +284,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kl * KPT + i;
-    if (live && kk < D) S_g[(size_t)kk * V + col] = S[i];
+    if (live && kk < D) S_g[(size_t)kk * S_step] = S[i];
   }
 }
 
@@ -294,7 +298,8 @@ int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
         return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
       }))
     return JV_ERR_UNSUPPORTED;
-  return jv_launch(kern, dim3(entries, p.heads, (p.V + SCAN_COLS - 1) / SCAN_COLS), dim3(SCAN_THREADS), smem, stream, p);
+  const int cols = p.V + ((!REMOVAL && p.state_n != nullptr) ? 1 : 0);
+  return jv_launch(kern, dim3(entries, p.heads, (cols + SCAN_COLS - 1) / SCAN_COLS), dim3(SCAN_THREADS), smem, stream, p);
 }
 
 template <bool REMOVAL, typename T>
@@ -313,18 +318,24 @@ template <typename T, typename W>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ o, const W* __restrict__ weight,
                                                              const T* __restrict__ gate, long long gate_stride,
                                                              T* __restrict__ out, long long out_stride, int heads, int V,
-                                                             float eps) {
+                                                             float eps, const float* __restrict__ gates) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
   const int n = blockIdx.x, h = blockIdx.y;
   const float* src = o + ((size_t)n * heads + h) * V;
+  // a matrix memory's output is first divided by max(|n . q|, exp(-m)) + 1e-6 (gates: [n, heads, 4] = (-, -, m, n . q))
+  float den = 1.f;
+  if (gates != nullptr) {
+    const float* g = gates + ((size_t)n * heads + h) * 4;
+    den = 1.f / (fmaxf(fabsf(g[3]), expf(-g[2])) + 1e-6f);
+  }
   float ss = 0.f;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) ss = fmaf(src[j], src[j], ss);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) ss = fmaf(src[j] * den, src[j] * den, ss);
   ss = block_sum(ss, scratch);
   const float inv = 1.f / sqrtf(ss / (float)V + eps);
   for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    float y = src[j] * inv * to_f32(weight[h * V + j]);
+    float y = src[j] * den * inv * to_f32(weight[h * V + j]);
     if (gate != nullptr) y *= 1.f / (1.f + expf(-to_f32(gate[(size_t)n * gate_stride + h * V + j])));
     out[(size_t)n * out_stride + h * V + j] = from_f32<T>(y);
   }
@@ -346,28 +357,36 @@ JV_EXPORT int jv_delta_prepare(const void* proj, int dtype, long long stride, in
 }
 
 // proj as above with q, k (heads * D each) and the two gates' pre-activations (heads each) at the given columns;
-// packed: [n, heads, 3, D] float; state_n, state_m: the normaliser and the running maximum of slot 0, rows
-// `slot_stride` floats apart.
+// gates: [n, heads, 4] float (keep, take, running maximum; the fourth place is left for the scan's n . q); packed:
+// [n, heads, 3, D] float; state_m: the running maximum of slot 0, rows `slot_stride` floats apart.
 JV_EXPORT int jv_memory_gates(const void* proj, int dtype, long long stride, int q_off, int k_off, int i_off, int f_off,
-                              const void* i_bias, const void* f_bias, int w_dtype, float cap, float q_scale, float* packed,
-                              float* state_n, float* state_m, long long slot_stride, const int* cu_seqlens,
-                              const int* slots, int n_slots, int entries, int heads, int D, int* status,
+                              const void* i_bias, const void* f_bias, int w_dtype, float cap, float q_scale, float* gates,
+                              float* packed, float* state_m, long long slot_stride, const int* cu_seqlens,
+                              const int* slots, int n_slots, int entries, int n, int heads, int D, int* status,
                               cudaStream_t stream) {
-  if (entries == 0) return JV_OK;
-  if (D > 32 * GATE_NPT) return JV_ERR_UNSUPPORTED;
-  JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, W, return jv_launch(
-      memory_gates_kernel<T, W>, dim3(entries, heads), dim3(32), 0, stream, (const T*)proj, stride, q_off, k_off, i_off,
-      f_off, (const W*)i_bias, (const W*)f_bias, cap, q_scale, packed, state_n, state_m, slot_stride, cu_seqlens, slots,
-      n_slots, heads, D, status)));
+  if (entries == 0 || n == 0) return JV_OK;
+  JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, W, {
+    const int rc = jv_launch(gate_scan_kernel<T, W>, dim3(entries, heads), dim3(32), 0, stream, (const T*)proj, stride,
+                             i_off, f_off, (const W*)i_bias, (const W*)f_bias, cap, gates, state_m, slot_stride,
+                             cu_seqlens, slots, n_slots, heads, status);
+    if (rc != JV_OK) return rc;
+    return jv_launch(memory_prepare_kernel<T>, dim3(n, heads), dim3(D > 64 ? 128 : 64), 0, stream, (const T*)proj, stride,
+                     q_off, k_off, q_scale, (const float*)gates, packed, heads, D);
+  }));
   return JV_ERR_UNSUPPORTED;
 }
 
 // The scan itself; `removal`: the packed rows hold (r, k, w, u, b), else (r, k, w).  v: rows of the projection.
+// state_n (or null; without removal only): [slots][heads * D], rows `slot_stride` apart, the state of one more column
+// whose value is 1 at every token; its outputs go to nq[(token * heads + head) * nq_stride].
 JV_EXPORT int jv_state_scan(const float* packed, int removal, const void* v, int dtype, long long v_stride, int v_off,
                             float* out, float* state, long long slot_stride, const int* cu_seqlens, const int* slots,
-                            int n_slots, int entries, int heads, int D, int V, int* status, cudaStream_t stream) {
+                            int n_slots, int entries, int heads, int D, int V, float* state_n, float* nq, int nq_stride,
+                            int* status, cudaStream_t stream) {
   if (entries == 0) return JV_OK;
+  if (state_n != nullptr && (removal || nq == nullptr)) return JV_ERR_UNSUPPORTED;
   ScanParams p;
+  p.state_n = state_n; p.nq = nq; p.nq_stride = nq_stride;
   p.packed = packed; p.v = v; p.v_stride = v_stride; p.v_off = v_off; p.out = out; p.state = state;
   p.slot_stride = slot_stride; p.cu_seqlens = cu_seqlens; p.slots = slots; p.n_slots = n_slots; p.heads = heads;
   p.D = D; p.V = V; p.status = status;
@@ -381,10 +400,10 @@ JV_EXPORT int jv_state_scan(const float* packed, int removal, const void* v, int
 // out: rows of `out_stride` elements, both of dtype `dtype`.
 JV_EXPORT int jv_head_norm_gate(const float* o, const void* weight, int w_dtype, const void* gate, long long gate_stride,
                                 void* out, int dtype, long long out_stride, int n, int heads, int V, float eps,
-                                cudaStream_t stream) {
+                                const float* gates, cudaStream_t stream) {
   if (n == 0) return JV_OK;
   JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, W, return jv_launch(
       head_norm_gate_kernel<T, W>, dim3(n, heads), dim3(V > 64 ? 128 : 64), 0, stream, o, (const W*)weight, (const T*)gate,
-      gate_stride, (T*)out, out_stride, heads, V, eps)));
+      gate_stride, (T*)out, out_stride, heads, V, eps, gates)));
   return JV_ERR_UNSUPPORTED;
 }

@@ -402,20 +402,10 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     value size]): key head g then reads value head g % value heads.  `score_cap` > 0 caps the scaled scores by
     cap * tanh(score / cap); `sigmoid` replaces the softmax by independent weights sigmoid(score + bias[query
     head]); `out` may be float32 whatever the type of q.  `head_scale` [query heads] multiplies the scaled scores of
-    its head; `dist_bias` [distances, query heads] is added to the score of a key that lies so many positions back
-    (the last row serves every larger distance); `sink` [query heads] adds exp(sink) once to the softmax's
+    its head; `dist_bias` [query heads, distances] is added to the score of a key that lies so many positions back
+    (the last column serves every larger distance); `sink` [query heads] adds exp(sink) once to the softmax's
     denominator."""
-    for t, nm in ((head_scale, "head_scale"), (sink, "sink")):
-        if t is not None:
-            _cuda(t, nm, torch.float32)
-            if t.numel() != n_q_heads:
-                raise KernelError(f"attn_simt: {nm} holds one number per query head")
-    n_dist = 0
-    if dist_bias is not None:
-        _cuda(dist_bias, "dist_bias", torch.float32)
-        if dist_bias.dim() != 2 or dist_bias.shape[1] != n_q_heads or dist_bias.shape[0] < 1:
-            raise KernelError("attn_simt: dist_bias is [distances, query heads]")
-        n_dist = dist_bias.shape[0]
+    n_dist = _score_extras("attn_simt", n_q_heads, head_scale, dist_bias, sink)
     for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, q.dtype, contiguous=(nm != "q"))
     _cuda(out, "out", contiguous=False)
@@ -453,6 +443,21 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
              _status_ptr(q.device), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
+def _score_extras(who: str, n_q_heads: int, head_scale, dist_bias, sink) -> int:
+    """Checks the per-head score options of the attention kernels; returns the number of distances of the bias table."""
+    for t, nm in ((head_scale, "head_scale"), (sink, "sink")):
+        if t is not None:
+            _cuda(t, nm, torch.float32)
+            if t.numel() != n_q_heads:
+                raise KernelError(f"{who}: {nm} holds one number per query head")
+    if dist_bias is None:
+        return 0
+    _cuda(dist_bias, "dist_bias", torch.float32)
+    if dist_bias.dim() != 2 or dist_bias.shape[0] != n_q_heads or dist_bias.shape[1] < 1:
+        raise KernelError(f"{who}: dist_bias is [query heads, distances]")
+    return dist_bias.shape[1]
+
+
 GENERAL_MMA_MAX_KEY, GENERAL_MMA_MAX_VALUE = 256, 128
 
 
@@ -475,9 +480,12 @@ def attn_general_mma_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
 def attn_general_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
                      n_work: int, n_q_heads: int, n_kv_heads: int, scale: float, split_size: int = 0, n_splits: int = 0,
-                     score_cap: float = 0.0, sigmoid: bool = False, bias: torch.Tensor | None = None) -> None:
+                     score_cap: float = 0.0, sigmoid: bool = False, bias: torch.Tensor | None = None,
+                     head_scale: torch.Tensor | None = None, dist_bias: torch.Tensor | None = None,
+                     sink: torch.Tensor | None = None) -> None:
     """Paged causal attention on the tensor cores with the options of `attn_simt`: the key size is the key
     cache's row, the value size and the value heads the value cache's; bfloat16 in, bfloat16 or float32 out."""
+    n_dist = _score_extras("attn_general_mma", n_q_heads, head_scale, dist_bias, sink)
     for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
     _cuda(out, "out", contiguous=False)
@@ -503,13 +511,13 @@ def attn_general_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache:
     f = _fn(attn_general_mma_library(key_dim, value_dim), "jv_attn_general_mma",
             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-             c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+             c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(part_o),
              _ptr(part_ml), _ptr(counters), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
              block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads,
              n_kv_heads, n_v_heads, key_dim, value_dim, k_cache.shape[1], k_cache.shape[0], 0, float(scale),
-             float(score_cap), 1 if sigmoid else 0, _ptr(bias), int(split_size), int(n_splits), _status_ptr(q.device),
-             _stream()), "attn_general_mma")
+             float(score_cap), 1 if sigmoid else 0, _ptr(bias), _ptr(head_scale), _ptr(dist_bias), n_dist, _ptr(sink),
+             int(split_size), int(n_splits), _status_ptr(q.device), _stream()), "attn_general_mma")
 
 
 def attn_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, positions: torch.Tensor,
@@ -723,10 +731,13 @@ def attn_tcgen05_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
 def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
                  n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, sigmoid: bool = False,
-                 bias: torch.Tensor | None = None) -> None:
+                 bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
+                 dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> None:
     """Paged causal attention of prompt portions on tcgen05 tensor cores with scores and output in tensor
     memory (csrc/attn_tcgen05.cu); `work` lists 128-row tiles of `attn_tcgen05_tokens_per_tile` tokens.  With
-    `sigmoid` the weight of a visible key is sigmoid(score * scale + bias[query head]) instead of a softmax."""
+    `sigmoid` the weight of a visible key is sigmoid(score * scale + bias[query head]) instead of a softmax;
+    `head_scale`, `dist_bias` and `sink` as for `attn_simt` (softmax only)."""
+    n_dist = _score_extras("attn_tcgen05", n_q_heads, head_scale, dist_bias, sink)
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm not in ("q", "out")))     # q and out may be some heads of wider rows
     if out.stride(1) != 1 or q.stride(1) != 1:
@@ -741,11 +752,13 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
             raise KernelError("attn_tcgen05: one bias per query head")
     f = _fn("attn_tcgen05", "jv_attn_tcgen05_ex", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                   c_float, c_int, c_void_p, c_void_p, c_void_p])
+                                                   c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                   c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
              n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1], k_cache.shape[0], float(scale),
-             1 if sigmoid else 0, _ptr(bias), _status_ptr(q.device), _stream()), "attn_tcgen05")
+             1 if sigmoid else 0, _ptr(bias), _ptr(head_scale), _ptr(dist_bias), n_dist, _ptr(sink),
+             _status_ptr(q.device), _stream()), "attn_tcgen05")
 
 
 DECODE_TCGEN05_MAX_REQUESTS = 512
@@ -1450,36 +1463,40 @@ def delta_prepare(proj: torch.Tensor, r_off: int, k_off: int, a_off: int, zw: to
 
 
 def memory_gates(proj: torch.Tensor, q_off: int, k_off: int, i_off: int, f_off: int, i_bias: torch.Tensor,
-                 f_bias: torch.Tensor, cap: float, q_scale: float, state_n: torch.Tensor, state_m: torch.Tensor,
-                 cu_seqlens: torch.Tensor, slots: torch.Tensor, n_entries: int, heads: int, dim: int) -> torch.Tensor:
-    """The gates of a matrix memory with exponential gating, scanned over every entry's tokens: updates the normaliser
-    `state_n` [slots, heads * dim] and the running maximum `state_m` [slots, heads] (views of the state rows, equal
-    row stride) and returns float32 [n, heads, 3, dim]: the query over its denominator, the key times its input
-    gate, the decay."""
+                 f_bias: torch.Tensor, cap: float, q_scale: float, state_m: torch.Tensor, cu_seqlens: torch.Tensor,
+                 slots: torch.Tensor, n_entries: int, heads: int, dim: int):
+    """The gates of a matrix memory with exponential gating: the running maximum `state_m` [slots, heads] (a view of
+    the state rows) is scanned over every entry's tokens, then all tokens at once are prepared.  Returns (packed
+    float32 [n, heads, 3, dim]: the scaled query, the key times its input gate, the decay; gates float32 [n, heads,
+    4]: decay, input gate, running maximum, and a place that `state_scan` fills with n . q)."""
     _cuda(proj, "proj", contiguous=False); _cuda(i_bias, "i_bias"); _cuda(f_bias, "f_bias", i_bias.dtype)
-    _cuda(state_n, "state_n", torch.float32, contiguous=False); _cuda(state_m, "state_m", torch.float32, contiguous=False)
+    _cuda(state_m, "state_m", torch.float32, contiguous=False)
     _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(slots, "slots", torch.int32)
     n = proj.shape[0]
-    if proj.stride(1) != 1 or state_n.stride(0) != state_m.stride(0) or state_n.stride(1) != 1 or \
-            state_n.shape[1] != heads * dim or state_m.shape[1] != heads or dim > SCAN_MAX_KEY:
+    if proj.stride(1) != 1 or state_m.stride(1) != 1 or state_m.shape[1] != heads or dim > SCAN_MAX_KEY or \
+            max(q_off, k_off) + heads * dim > proj.shape[1] or max(i_off, f_off) + heads > proj.shape[1]:
         raise KernelError("memory_gates: shapes do not fit")
     packed = torch.empty((n, heads, 3, dim), dtype=torch.float32, device=proj.device)
+    gates = torch.empty((n, heads, 4), dtype=torch.float32, device=proj.device)
     f = _fn("recurrent", "jv_memory_gates", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                              c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
-                                             c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(proj.data_ptr(), _code(proj, "proj"), proj.stride(0), q_off, k_off, i_off, f_off, i_bias.data_ptr(),
-             f_bias.data_ptr(), _code(i_bias, "i_bias"), float(cap), float(q_scale), packed.data_ptr(), state_n.data_ptr(),
-             state_m.data_ptr(), state_n.stride(0), cu_seqlens.data_ptr(), slots.data_ptr(), state_n.shape[0], n_entries,
-             heads, dim, _status_ptr(proj.device), _stream()), "memory_gates")
-    return packed
+             f_bias.data_ptr(), _code(i_bias, "i_bias"), float(cap), float(q_scale), gates.data_ptr(), packed.data_ptr(),
+             state_m.data_ptr(), state_m.stride(0), cu_seqlens.data_ptr(), slots.data_ptr(), state_m.shape[0], n_entries,
+             n, heads, dim, _status_ptr(proj.device), _stream()), "memory_gates", launches=2)
+    return packed, gates
 
 
 def state_scan(packed: torch.Tensor, v: torch.Tensor, v_off: int, state: torch.Tensor, cu_seqlens: torch.Tensor,
-               slots: torch.Tensor, n_entries: int, value_dim: int) -> torch.Tensor:
+               slots: torch.Tensor, n_entries: int, value_dim: int, state_n: torch.Tensor | None = None,
+               gates: torch.Tensor | None = None) -> torch.Tensor:
     """S <- diag(w) S - b (u^T S) + k v^T and o = S^T r, token after token of every entry, for the per-head states
     `state` [slots, >= heads * dim * value_dim] float32 (a view of the state rows); `packed` [n, heads, 5 or 3, dim]
     holds (r, k, w, u, b) or, without the removal term, (r, k, w); the values are columns `v_off`.. of the rows of
-    `v`.  Returns o [n, heads * value_dim] float32."""
+    `v`.  Returns o [n, heads * value_dim] float32.  With `state_n` [slots, heads * dim] (a view of the same rows) the
+    state has one more column whose value is 1 at every token (a normaliser n <- w n + k); its output n . r goes to
+    the fourth place of `gates` [n, heads, 4]."""
     _cuda(packed, "packed", torch.float32); _cuda(v, "v", contiguous=False)
     _cuda(state, "state", torch.float32, contiguous=False)
     _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(slots, "slots", torch.int32)
@@ -1487,21 +1504,29 @@ def state_scan(packed: torch.Tensor, v: torch.Tensor, v_off: int, state: torch.T
     if nv not in (3, 5) or v.shape[0] != n or v.stride(1) != 1 or v_off + heads * value_dim > v.shape[1] or \
             state.stride(1) != 1 or state.shape[1] < heads * dim * value_dim or dim > SCAN_MAX_KEY:
         raise KernelError("state_scan: shapes do not fit")
+    nq = None
+    if state_n is not None:
+        _cuda(state_n, "state_n", torch.float32, contiguous=False); _cuda(gates, "gates", torch.float32)
+        if nv != 3 or state_n.stride(0) != state.stride(0) or state_n.stride(1) != 1 or state_n.shape[1] != heads * dim or \
+                state_n.shape[0] != state.shape[0] or tuple(gates.shape) != (n, heads, 4):
+            raise KernelError("state_scan: the normaliser does not fit")
+        nq = gates.data_ptr() + 3 * 4
     out = torch.empty((n, heads * value_dim), dtype=torch.float32, device=packed.device)
     f = _fn("recurrent", "jv_state_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p,
                                            c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                           c_void_p])
+                                           c_void_p, c_int, c_void_p, c_void_p])
     _check(f(packed.data_ptr(), 1 if nv == 5 else 0, v.data_ptr(), _code(v, "v"), v.stride(0), v_off, out.data_ptr(),
              state.data_ptr(), state.stride(0), cu_seqlens.data_ptr(), slots.data_ptr(), state.shape[0], n_entries, heads,
-             dim, value_dim, _status_ptr(packed.device), _stream()), "state_scan")
+             dim, value_dim, _ptr(state_n), nq, 4, _status_ptr(packed.device), _stream()), "state_scan")
     return out
 
 
 def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, heads: int,
-                   value_dim: int, eps: float) -> torch.Tensor:
+                   value_dim: int, eps: float, gates: torch.Tensor | None = None) -> torch.Tensor:
     """Each head of `o` [n, heads * value_dim] float32 divided by its root mean square, times `weight` [heads *
     value_dim], times sigmoid(gate) (rows of `out`'s type, possibly a column range), written to `out` (possibly a
-    column range)."""
+    column range).  With `gates` [n, heads, 4] = (-, -, m, n . q) each head is first divided by
+    max(|n . q|, exp(-m)) + 1e-6."""
     _cuda(o, "o", torch.float32); _cuda(weight, "weight"); _cuda(out, "out", contiguous=False)
     n = o.shape[0]
     if o.shape[1] != heads * value_dim or out.shape != o.shape or out.stride(1) != 1 or weight.numel() != o.shape[1]:
@@ -1512,10 +1537,14 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | N
         if gate.shape != o.shape or gate.stride(1) != 1:
             raise KernelError("head_norm_gate: the gate has the heads' shape")
         g_stride = gate.stride(0)
+    if gates is not None:
+        _cuda(gates, "gates", torch.float32)
+        if tuple(gates.shape) != (n, heads, 4):
+            raise KernelError("head_norm_gate: gates are [n, heads, 4]")
     f = _fn("recurrent", "jv_head_norm_gate", [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_longlong,
-                                               c_int, c_int, c_int, c_float, c_void_p])
+                                               c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check(f(o.data_ptr(), weight.data_ptr(), _code(weight, "weight"), _ptr(gate), g_stride, out.data_ptr(),
-             _code(out, "out"), out.stride(0), n, heads, value_dim, float(eps), _stream()), "head_norm_gate")
+             _code(out, "out"), out.stride(0), n, heads, value_dim, float(eps), _ptr(gates), _stream()), "head_norm_gate")
     return out
 
 

@@ -76,7 +76,7 @@ class GeneralAttention(Part):
         # tcgen05 kernels for heads of 128, mma.sync for 16/32/64, in bfloat16).  Every other bfloat16 mixer with
         # sizes in steps of 16 takes the tensor-core kernel compiled for its pair of sizes; the rest, and 32-bit,
         # the CUDA-core kernel.
-        # a temperature per head, a bias by distance and a sink are options of the CUDA-core kernel
+        # a temperature per head, a bias by distance and a sink are options of both of these
         self.extras = spec.head_temperature or spec.distance_bias is not None or spec.sink
         if self.extras and (spec.twin is not None or (spec.sink and spec.weights != "softmax")):
             raise ValueError("head temperature, distance bias and sink are built for one softmax map")
@@ -87,13 +87,14 @@ class GeneralAttention(Part):
             self.plain = Attention(AttentionSpec(spec.hidden_size, self.hq, self.hk, self.d, spec.scale, prefix=""),
                                    self.prefix, ctx)
             self.kernels += tuple(k for k in self.plain.kernels if k not in self.kernels and k != "rope_kv")
-        elif not self.extras and ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
+        elif ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
             self.general = ops.attn_general_mma_library(self.d, self.dv)
             self.kernels += (self.general,)
-        # sigmoid weights on heads of 128: prompt portions that fill a 128-row tile go to the tcgen05 kernel
-        self.sigmoid_tiles = (self.general is not None and spec.weights == "sigmoid" and not spec.score_cap
-                              and self.hv == self.hk and self.dv == self.d == 128)
-        if self.sigmoid_tiles:
+        # heads of 128 with sigmoid weights, or with a softmax that has a temperature per head, a bias by distance or a
+        # sink: prompt portions that fill a 128-row tile go to the tcgen05 kernel
+        self.big_tiles = (self.general is not None and not spec.score_cap and self.hv == self.hk and self.dv == self.d == 128
+                          and spec.twin is None and (spec.weights == "sigmoid") != bool(self.extras))
+        if self.big_tiles:
             self.kernels += ("attn_tcgen05",)
         self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
         self.head_scale = self.dist_bias = self.sink = None
@@ -164,10 +165,10 @@ class GeneralAttention(Part):
         if s.head_temperature:
             self.head_scale = tensors[n["temp"]].to(torch.float32).contiguous()
         if s.distance_bias is not None:
-            # the table by distance, not by bucket: the kernel indexes it with min(distance, last row)
+            # the table by head and distance, not by bucket: the kernels index a head's row with min(distance, last)
             rel = tensors[n["rel"]].to(torch.float32)
             rows = distance_buckets(rel.shape[0], int(s.distance_bias[1]))
-            self.dist_bias = rel[torch.tensor(rows, device=rel.device)].contiguous()
+            self.dist_bias = rel[torch.tensor(rows, device=rel.device)].t().contiguous()
         if s.sink:
             self.sink = tensors[n["sink"]].to(torch.float32).contiguous()
         if s.twin is not None:
@@ -185,7 +186,7 @@ class GeneralAttention(Part):
             return self.plain.tile_classes(page_size)
         if self.general is not None:
             small = ops.attn_general_mma_tokens_per_tile(self.hq, self.hk)
-            if self.sigmoid_tiles and ops.attn_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hk, page_size, 0):
+            if self.big_tiles and ops.attn_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hk, page_size, 0):
                 big = ops.attn_tcgen05_tokens_per_tile(self.hq, self.hk)
                 if big > small:
                     return [(small, 2, big), (big, big, self.FOREVER)]
@@ -256,7 +257,8 @@ class GeneralAttention(Part):
             work, n_work = step.tile_work[cls]
             if n_work and cls[1] > 2:                      # the class of whole 128-row tiles
                 ops.attn_tcgen05(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, s.scale,
-                                 sigmoid=True, bias=self.bias)
+                                 sigmoid=s.weights == "sigmoid", bias=self.bias, head_scale=self.head_scale,
+                                 dist_bias=self.dist_bias, sink=self.sink)
             elif n_work:
                 kernel(work, n_work)
         dwork, n_dec = step.decode_work

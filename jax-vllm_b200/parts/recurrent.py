@@ -137,11 +137,13 @@ class MatrixMemory(_StateMixer):
         hd, hv, h = self.hd, self.hv, self.h
         state = cache.state
         mats = hd * self.dv
-        packed = ops.memory_gates(row, 0, hd, 2 * hd + 2 * hv, 2 * hd + 2 * hv + h, self.i_bias, self.f_bias,
-                                  self.spec.gate_cap, self.d ** -0.5, state[:, mats:mats + hd], state[:, mats + hd:],
-                                  step.cu_seqlens, step.state_slots, step.n_entries, h, self.d)
-        o = ops.state_scan(packed, row, 2 * hd, state, step.cu_seqlens, step.state_slots, step.n_entries, self.dv)
-        return ops.head_norm_gate(o, self.norm, row[:, 2 * hd + hv:2 * hd + 2 * hv], out, h, self.dv, self.spec.norm_eps)
+        packed, gates = ops.memory_gates(row, 0, hd, 2 * hd + 2 * hv, 2 * hd + 2 * hv + h, self.i_bias, self.f_bias,
+                                         self.spec.gate_cap, self.d ** -0.5, state[:, mats + hd:], step.cu_seqlens,
+                                         step.state_slots, step.n_entries, h, self.d)
+        o = ops.state_scan(packed, row, 2 * hd, state, step.cu_seqlens, step.state_slots, step.n_entries, self.dv,
+                           state_n=state[:, mats:mats + hd], gates=gates)
+        return ops.head_norm_gate(o, self.norm, row[:, 2 * hd + hv:2 * hd + 2 * hv], out, h, self.dv, self.spec.norm_eps,
+                                  gates=gates)
 
 
 register_mixer("matrix_memory", MatrixMemory)

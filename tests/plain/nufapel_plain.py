@@ -81,6 +81,25 @@ def run_order(cfg: dict):
 
 
 # -------------------------------------------------------------------- general_delta
+def delta_scan(r, k, v, w, a, S=None):
+    """The generalized delta rule over T tokens.  r, k, w, a [T, H, D], v [T, H, V]; S [H, D, V] (zero if None).
+    Returns (o [T, H, V], the state after the last token)."""
+    T, H, D = k.shape
+    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    S = torch.zeros(H, D, v.shape[-1], dtype=k.dtype) if S is None else S.clone()
+    o = torch.zeros(T, H, v.shape[-1], dtype=k.dtype)
+    for t in range(T):
+        uS = torch.einsum("hk,hkv->hv", u[t], S)                      # u^T S, the old state
+        S = w[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hkv,hk->hv", S, r[t])
+    return o, S
+
+
+def delta_decay(z):
+    """The decay per channel from its pre-activation (bias included)."""
+    return torch.exp(-math.exp(-0.5) * torch.sigmoid(z))
+
+
 def general_delta(h, W, p, mx, eps):
     """h [T, width] -> [T, width]; p the tensor prefix '<layer>.mix'."""
     H, D = int(mx["heads"]), int(mx["dim"])
@@ -88,16 +107,9 @@ def general_delta(h, W, p, mx, eps):
     r = (h @ W[f"{p}.r"].T).view(T, H, D)
     k = (h @ W[f"{p}.k"].T).view(T, H, D)
     v = (h @ W[f"{p}.v"].T).view(T, H, D)
-    lora = torch.tanh(h @ W[f"{p}.w1"].T) @ W[f"{p}.w2"].T + W[f"{p}.w0"]
-    w = torch.exp(-math.exp(-0.5) * torch.sigmoid(lora)).view(T, H, D)
+    w = delta_decay(torch.tanh(h @ W[f"{p}.w1"].T) @ W[f"{p}.w2"].T + W[f"{p}.w0"]).view(T, H, D)
     a = torch.sigmoid(h @ W[f"{p}.a"].T + W[f"{p}.a.b"]).view(T, H, D)
-    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    S = torch.zeros(H, D, D, dtype=h.dtype)
-    o = torch.zeros(T, H, D, dtype=h.dtype)
-    for t in range(T):
-        uS = torch.einsum("hk,hkv->hv", u[t], S)                      # u^T S, the old state
-        S = w[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hkv,hk->hv", S, r[t])
+    o, _ = delta_scan(r, k, v, w, a)
     o = unit(o, eps).reshape(T, H * D) * W[f"{p}.norm"]
     return (o * torch.sigmoid(h @ W[f"{p}.g"].T)) @ W[f"{p}.o"].T
 
@@ -110,6 +122,24 @@ def distance_bucket(n: int, B: int, D: int) -> int:
     return min(B - 1, half + int(math.floor(math.log(n / half) / math.log(D / half) * (B - half))))
 
 
+def biased_sink_attend(q, k, v, scale, temp, rel, bias_max, sink, first=0):
+    """q [Tq, H, D] at positions first .. first + Tq - 1 against k [T, H, D], v [T, H, V] at positions 0 .. T - 1
+    (causal).  score = q.k * scale * temp_h + rel[bucket(i - j), h]; the softmax's denominator also holds exp(sink_h),
+    which has no value.  Returns [Tq, H, V]."""
+    Tq, T, B = q.shape[0], k.shape[0], rel.shape[0]
+    buckets = torch.tensor([[distance_bucket(first + i - j, B, bias_max) if j <= first + i else 0 for j in range(T)]
+                            for i in range(Tq)])
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale * temp[:, None, None]
+    s = s + rel[buckets].permute(2, 0, 1)
+    hidden = torch.arange(T)[None, :] > (first + torch.arange(Tq))[:, None]
+    s = s.masked_fill(hidden, -math.inf)
+    sk = sink[:, None, None]
+    m = torch.maximum(s.max(dim=-1, keepdim=True).values, sk)
+    e = torch.exp(s - m)
+    weights = e / (e.sum(-1, keepdim=True) + torch.exp(sk - m))
+    return torch.einsum("hij,jhv->ihv", weights, v)
+
+
 def sink_attention(h, W, p, mx):
     """Causal softmax attention with a learned distance bias, a temperature per head and a sink in the denominator;
     p the tensor prefix '<layer>.mix.left'.  Returns the projected output [T, width]."""
@@ -118,37 +148,27 @@ def sink_attention(h, W, p, mx):
     q = (h @ W[f"{p}.q"].T).view(T, H, D)
     k = (h @ W[f"{p}.k"].T).view(T, G, D).repeat_interleave(H // G, dim=1)
     v = (h @ W[f"{p}.v"].T).view(T, G, V).repeat_interleave(H // G, dim=1)
-    rel = W[f"{p}.rel"]
-    B = rel.shape[0]
-    buckets = torch.tensor([[distance_bucket(i - j, B, int(mx["bias_max"])) if j <= i else 0 for j in range(T)]
-                            for i in range(T)])
-    s = torch.einsum("ihd,jhd->hij", q, k) * float(mx["scale"]) * W[f"{p}.temp"][:, None, None]
-    s = s + rel[buckets].permute(2, 0, 1)
-    s = s.masked_fill(torch.ones(T, T).triu(1).bool(), -math.inf)
-    sink = W[f"{p}.sink"][:, None, None]
-    m = torch.maximum(s.max(dim=-1, keepdim=True).values, sink)
-    e = torch.exp(s - m)
-    weights = e / (e.sum(-1, keepdim=True) + torch.exp(sink - m))
-    o = torch.einsum("hij,jhv->ihv", weights, v)
+    o = biased_sink_attend(q, k, v, float(mx["scale"]), W[f"{p}.temp"], W[f"{p}.rel"], int(mx["bias_max"]), W[f"{p}.sink"])
     o = o * torch.sigmoid(h @ W[f"{p}.g"].T)[:, :, None]
     return o.reshape(T, H * V) @ W[f"{p}.o"].T
 
 
 # ----------------------------------------------------------------- parallel: right
-def matrix_memory(h, W, p, mx, eps):
-    """Matrix memory with exponential input gate and sigmoid forget gate in the log domain; p the tensor prefix
-    '<layer>.mix.right'."""
-    H, D, V, cap = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"]), float(mx["gate_cap"])
-    T = h.shape[0]
-    q = (h @ W[f"{p}.q"].T).view(T, H, D) * D ** -0.5
-    k = (h @ W[f"{p}.k"].T).view(T, H, D)
-    v = (h @ W[f"{p}.v"].T).view(T, H, V)
-    gi = cap * torch.tanh((h @ W[f"{p}.i"].T + W[f"{p}.i.b"]) / cap)
-    gf = F.logsigmoid(cap * torch.tanh((h @ W[f"{p}.f"].T + W[f"{p}.f.b"]) / cap))
-    S = torch.zeros(H, D, V, dtype=h.dtype)
-    n = torch.zeros(H, D, dtype=h.dtype)
-    m = torch.zeros(H, dtype=h.dtype)
-    o = torch.zeros(T, H, V, dtype=h.dtype)
+def capped_gates(zi, zf, cap):
+    """Log input gate and log forget gate from their pre-activations (biases included)."""
+    return cap * torch.tanh(zi / cap), F.logsigmoid(cap * torch.tanh(zf / cap))
+
+
+def memory_scan(q, k, v, gi, gf, state=None):
+    """The matrix memory over T tokens.  q (already scaled), k [T, H, D], v [T, H, V], gi, gf [T, H] (log gates);
+    state = (S [H, D, V], n [H, D], m [H]), all zero if None.  Returns (o [T, H, V], the state after the last token)."""
+    T, H, D = k.shape
+    V = v.shape[-1]
+    if state is None:
+        S, n, m = torch.zeros(H, D, V, dtype=k.dtype), torch.zeros(H, D, dtype=k.dtype), torch.zeros(H, dtype=k.dtype)
+    else:
+        S, n, m = (t.clone() for t in state)
+    o = torch.zeros(T, H, V, dtype=k.dtype)
     for t in range(T):
         m_new = torch.maximum(gf[t] + m, gi[t])
         keep, take = torch.exp(gf[t] + m - m_new), torch.exp(gi[t] - m_new)
@@ -157,6 +177,19 @@ def matrix_memory(h, W, p, mx, eps):
         m = m_new
         den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-m)) + 1e-6
         o[t] = torch.einsum("hkv,hk->hv", S, q[t]) / den[:, None]
+    return o, (S, n, m)
+
+
+def matrix_memory(h, W, p, mx, eps):
+    """Matrix memory with exponential input gate and sigmoid forget gate in the log domain; p the tensor prefix
+    '<layer>.mix.right'."""
+    H, D, V, cap = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"]), float(mx["gate_cap"])
+    T = h.shape[0]
+    q = (h @ W[f"{p}.q"].T).view(T, H, D) * D ** -0.5
+    k = (h @ W[f"{p}.k"].T).view(T, H, D)
+    v = (h @ W[f"{p}.v"].T).view(T, H, V)
+    gi, gf = capped_gates(h @ W[f"{p}.i"].T + W[f"{p}.i.b"], h @ W[f"{p}.f"].T + W[f"{p}.f.b"], cap)
+    o, _ = memory_scan(q, k, v, gi, gf)
     o = unit(o, eps).reshape(T, H * V) * W[f"{p}.norm"]
     return (o * torch.sigmoid(h @ W[f"{p}.g"].T)) @ W[f"{p}.o"].T
 
@@ -172,17 +205,28 @@ def dense_ff(h, W, p):
     return gelu_erf(h @ W[f"{p}.up"].T) @ W[f"{p}.down"].T
 
 
-def route(z, top: int, groups: int, keep: int, scale: float):
-    """z [T, E] router logits -> (chosen experts [T, top], their weights [T, top])."""
+def route(z, top: int, groups: int, keep: int, scale: float, margins=None):
+    """z [T, E] router logits -> (chosen experts [T, top], their weights [T, top]).  `margins`, a list, receives
+    per token the smallest difference of scores on which a choice hangs (the last kept group against the best one
+    dropped, the last chosen expert against the best one left)."""
     T, E = z.shape
     s = torch.sigmoid(z)
     per = E // groups
     gs = s.view(T, groups, per).topk(min(2, per), dim=-1).values.sum(-1)
-    kept = gs.topk(keep, dim=-1).indices
+    ranked = gs.topk(groups, dim=-1)
+    kept = ranked.indices[:, :keep]
     allowed = torch.zeros(T, groups, dtype=torch.bool).scatter_(1, kept, True).repeat_interleave(per, dim=1)
     masked = torch.where(allowed, s, torch.full_like(s, -1.0))
-    idx = masked.topk(top, dim=-1).indices
+    best = masked.topk(min(top + 1, keep * per), dim=-1)
+    idx = best.indices[:, :top]
     chosen = s.gather(1, idx)
+    if margins is not None:
+        m = torch.full((T,), float("inf"), dtype=z.dtype)
+        if keep < groups:
+            m = torch.minimum(m, ranked.values[:, keep - 1] - ranked.values[:, keep])
+        if best.values.shape[1] > top:
+            m = torch.minimum(m, best.values[:, top - 1] - best.values[:, top])
+        margins.append(m)
     return idx, chosen / (chosen.sum(-1, keepdim=True) + 1e-20) * scale
 
 
@@ -192,10 +236,10 @@ def expert(h, W, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W[f"{p}.down"].T
 
 
-def routed_ff(h, W, p, ml, router_input=None):
+def routed_ff(h, W, p, ml, margins=None):
     ro = ml["router"]
-    z = (h if router_input is None else router_input) @ W[f"{p}.router"].T
-    idx, wt = route(z, int(ro["top"]), int(ro["groups"]["count"]), int(ro["groups"]["keep"]), float(ro["scale"]))
+    z = h @ W[f"{p}.router"].T
+    idx, wt = route(z, int(ro["top"]), int(ro["groups"]["count"]), int(ro["groups"]["keep"]), float(ro["scale"]), margins)
     out = torch.zeros_like(h)
     for e in range(int(ro["experts"])):
         hit = (idx == e)
@@ -207,8 +251,9 @@ def routed_ff(h, W, p, ml, router_input=None):
 
 
 # ------------------------------------------------------------------------ the model
-def forward(cfg: dict, W: dict, tokens, taps=None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence run whole.  `taps`, a list, receives the stream after every layer run."""
+def forward(cfg: dict, W: dict, tokens, taps=None, margins=None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence run whole.  `taps`, a list, receives the stream after every layer run;
+    `margins`, a list, one tensor [T] per routed feed-forward that ran (see `route`)."""
     eps = float(cfg["norm"]["eps"])
     T = len(tokens)
     x = W["embed"][torch.tensor(tokens)] + W["pos"][:T]
@@ -227,9 +272,10 @@ def forward(cfg: dict, W: dict, tokens, taps=None) -> torch.Tensor:
         ml = layer.get("mlp")
         if ml is not None:
             h = dyt(x, W, f"{p}.norm2")
-            y = dense_ff(h, W, f"{p}.mlp") if ml["kind"] == "dense" else routed_ff(h, W, f"{p}.mlp", ml)
+            y = dense_ff(h, W, f"{p}.mlp") if ml["kind"] == "dense" else routed_ff(h, W, f"{p}.mlp", ml, margins)
             x = x + torch.sigmoid(h @ W[f"{p}.rg2"].T + W[f"{p}.rg2.b"]) * y
         if taps is not None:
             taps.append(x.clone())
-    cap = float(cfg["logit_softcap"])
-    return cap * torch.tanh((dyt(x, W, "final.norm") @ W["head"].T) / cap)
+    logits = dyt(x, W, "final.norm") @ W["head"].T
+    cap = cfg.get("logit_softcap")
+    return logits if cap is None else float(cap) * torch.tanh(logits / float(cap))
