@@ -160,8 +160,33 @@ struct ScanParams {
   // one more column, number V, with the value 1 for every token (the normaliser of a matrix memory): its state is
   // state_n [slots][heads * D] (rows `slot_stride` apart) and its output goes to nq[(token * heads + head) * nq_stride]
   float* state_n; float* nq; int nq_stride;
+  // Long entries in segments (mode 0: every entry whole, one block column an entry).  An entry of len tokens has
+  // max(1, ceil(len / seg_len)) segments; the segments of all entries are numbered in the entries' order and
+  // blockIdx.x is a segment's number.  The columns of a segment's buffer, [D][v_tot] floats at (segment * heads +
+  // head) * D * v_tot: the V value columns, the normaliser's (if any), then what the segment does to a state that
+  // comes in: with the removal term D columns that start as the identity and take no value (the product of the
+  // tokens' transitions), without it one column that starts as ones (the product of the decays, channel by channel).
+  //   mode 1  every segment but an entry's last runs from a zero state and writes its buffer in seg_local; no output
+  //   (then scan_combine_kernel chains them: seg_start[s + 1] = transition(s) seg_start[s] + local(s))
+  //   mode 2  every segment runs from seg_start (an entry's first: from the state) and writes the outputs; an entry's
+  //           last segment writes the state
+  int mode, seg_len, n_entries, v_tot;
+  float* seg_local; float* seg_start;
   int* status;
 };
+
+// Which entry and which of its segments the segment number g is; false if there is no such segment.
+__device__ __forceinline__ bool find_segment(const int* __restrict__ cu_seqlens, int n_entries, int seg_len, int g,
+                                             int& entry, int& seg, int& n_seg) {
+  int acc = 0;
+  for (int e = 0; e < n_entries; ++e) {
+    const int len = cu_seqlens[e + 1] - cu_seqlens[e];
+    const int ns = max(1, (len + seg_len - 1) / seg_len);
+    if (g < acc + ns) { entry = e; seg = g - acc; n_seg = ns; return true; }
+    acc += ns;
+  }
+  return false;
+}
 
 constexpr int SCAN_THREADS = 128;    // 4 warps of 8 columns x 4 key lanes
 constexpr int SCAN_COLS = 32;
@@ -175,6 +200,10 @@ __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
@@ -185,12 +214,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
   extern __shared__ __align__(16) float smem[];       // [2][CHUNK][NV][ROW]
   pdl_trigger();
   pdl_wait();
-  const int entry = blockIdx.x, h = blockIdx.y;
+  const int h = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kl = lane >> 3;                            // which quarter of the key channels
   const int col = blockIdx.z * SCAN_COLS + warp * 8 + (lane & 7);
   const int D = p.D, V = p.V;
-  const int t0 = p.cu_seqlens[entry], t1 = p.cu_seqlens[entry + 1];
+  int entry = blockIdx.x, seg = 0, n_seg = 1;
+  if (p.mode != 0 && !find_segment(p.cu_seqlens, p.n_entries, p.seg_len, blockIdx.x, entry, seg, n_seg)) return;
+  if (p.mode == 1 && seg == n_seg - 1) return;         // nothing follows an entry's last segment
+  int t0 = p.cu_seqlens[entry], t1 = p.cu_seqlens[entry + 1];
+  if (p.mode != 0) {
+    t0 += seg * p.seg_len;
+    t1 = min(t1, t0 + p.seg_len);
+  }
   const int slot = p.slots[entry];
   if (slot < 0 || slot >= p.n_slots) {
     if (tid == 0) atomicOr(p.status, JV_STATUS_BAD_ROW);
@@ -198,16 +234,27 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
   }
   if (t0 >= t1) return;
   const bool is_n = !REMOVAL && p.state_n != nullptr && col == V;
-  const bool live = col < V || is_n;
-  // element kk of this thread's column: S_g[kk * S_step]
+  const int v_n = V + ((!REMOVAL && p.state_n != nullptr) ? 1 : 0);   // columns that belong to the state
+  const int tcol = col - v_n;                          // mode 1: which column of the transition this thread carries
+  const bool is_t = p.mode == 1 && tcol >= 0 && col < p.v_tot;
+  const bool live = col < V || is_n || is_t;
+  // element kk of this thread's column: S_g[kk * S_step] in the state, B_g[kk * v_tot] in a segment's buffer
   float* S_g = is_n ? p.state_n + (size_t)slot * p.slot_stride + (size_t)h * D
                     : p.state + (size_t)slot * p.slot_stride + (size_t)h * D * V + col;
   const size_t S_step = is_n ? 1 : V;
+  const size_t B_off = ((size_t)blockIdx.x * p.heads + h) * D * p.v_tot + col;
+  const bool from_state = p.mode == 0 || (p.mode == 2 && seg == 0);
+  const bool to_state = p.mode == 0 || (p.mode == 2 && seg == n_seg - 1);
   float S[KPT];
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kl * KPT + i;
-    S[i] = (live && kk < D) ? S_g[(size_t)kk * S_step] : 0.f;
+    float s0 = 0.f;
+    if (live && kk < D) {
+      if (p.mode == 1) s0 = is_t ? ((REMOVAL ? kk == tcol : true) ? 1.f : 0.f) : 0.f;
+      else s0 = from_state ? S_g[(size_t)kk * S_step] : p.seg_start[B_off + (size_t)kk * p.v_tot];
+    }
+    S[i] = s0;
   }
   for (int i = tid; i < 2 * CHUNK * NV * ROW; i += SCAN_THREADS) smem[i] = 0.f;     // the padding stays zero
   __syncthreads();
@@ -217,11 +264,25 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
     // vectors of tokens first .. first + CHUNK - 1 (those that exist) into buffer `buf`
     const int tokens = min(CHUNK, t1 - first);
     const int per_token = NV * D;
-    for (int i = tid; i < tokens * per_token; i += SCAN_THREADS) {
-      const int t = i / per_token, r = i - t * per_token;
-      const int v = r / D, kk = r - v * D;
-      float* dst = smem + ((size_t)(buf * CHUNK + t) * NV + v) * ROW + (kk / KPT) * (KPT + 4) + kk % KPT;
-      cp_async_4(dst, p.packed + ((size_t)(first + t) * p.heads + h) * per_token + r);
+    // a lane's KPT channels are a run in both places: 16 bytes a copy where the key size allows (rows of the packed
+    // tensor then start on 16-byte boundaries), 4 bytes otherwise
+    if ((D & 3) == 0) {
+      // QP = 4 * KPT / 4 threads take a vector's 16-byte pieces, SCAN_THREADS / QP vectors at a time
+      constexpr int QP = KPT, ROWS = SCAN_THREADS / QP;
+      const int kk = (tid % QP) * 4, sub = tid / QP;
+      if (kk < D) {
+        float* dst = smem + (size_t)buf * CHUNK * NV * ROW + (kk / KPT) * (KPT + 4) + kk % KPT;
+        const float* src = p.packed + ((size_t)first * p.heads + h) * per_token + kk;
+        for (int tv = sub; tv < tokens * NV; tv += ROWS)
+          cp_async_16(dst + tv * ROW, src + (size_t)(tv / NV) * p.heads * per_token + (tv % NV) * D);
+      }
+    } else {
+      for (int tv = 0; tv < tokens * NV; ++tv) {
+        float* row = smem + (size_t)(buf * CHUNK * NV + tv) * ROW;
+        const float* src = p.packed + ((size_t)(first + tv / NV) * p.heads + h) * per_token + (tv % NV) * D;
+        for (int kk = tid; kk < D; kk += SCAN_THREADS)
+          cp_async_4(row + (kk / KPT) * (KPT + 4) + kk % KPT, src + kk);
+      }
     }
     cp_async_commit();
   };
@@ -229,7 +290,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
   auto fetch_v = [&](float* dst, int first) {
 #pragma unroll
     for (int t = 0; t < CHUNK; ++t)
-      dst[t] = is_n ? 1.f : (first + t < t1) ? to_f32(vsrc[(size_t)(first + t) * p.v_stride]) : 0.f;
+      dst[t] = is_n ? 1.f : (col < V && first + t < t1) ? to_f32(vsrc[(size_t)(first + t) * p.v_stride]) : 0.f;
   };
   stage(0, t0);
   fetch_v(vr, t0);
@@ -273,7 +334,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
       }
       o += __shfl_xor_sync(0xffffffffu, o, 8);
       o += __shfl_xor_sync(0xffffffffu, o, 16);
-      if (kl == 0 && live) {
+      if (kl == 0 && live && p.mode != 1) {
         if (is_n) p.nq[((size_t)(first + t) * p.heads + h) * p.nq_stride] = o;
         else p.out[(size_t)(first + t) * p.heads * V + (size_t)h * V + col] = o;
       }
@@ -284,7 +345,123 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanPara
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kl * KPT + i;
-    if (live && kk < D) S_g[(size_t)kk * S_step] = S[i];
+    if (live && kk < D) {
+      if (p.mode == 1) p.seg_local[B_off + (size_t)kk * p.v_tot] = S[i];
+      else if (to_state) S_g[(size_t)kk * S_step] = S[i];
+    }
+  }
+}
+
+// Chains the segments of an entry: from the state that the entry brings, seg_start[s + 1] = T_s seg_start[s] + local_s,
+// where T_s is what segment s does to a state that comes in (seg_local's last columns).
+// Without the removal term T_s is diagonal (one column of decay products): every element of the state is a chain of
+// its own, one thread an element, grid (entry, head, blocks over D * columns).
+__global__ void __launch_bounds__(128) scan_combine_diag_kernel(const ScanParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int entry = blockIdx.x, h = blockIdx.y;
+  const int D = p.D, V = p.V;
+  const int v_n = V + (p.state_n != nullptr ? 1 : 0);
+  const int idx = blockIdx.z * 128 + threadIdx.x;
+  if (idx >= D * v_n) return;
+  const int kk = idx / v_n, col = idx - kk * v_n;
+  const int len = p.cu_seqlens[entry + 1] - p.cu_seqlens[entry];
+  const int n_seg = max(1, (len + p.seg_len - 1) / p.seg_len);
+  if (n_seg < 2) return;
+  const int slot = p.slots[entry];
+  if (slot < 0 || slot >= p.n_slots) return;             // the scan reports it
+  int g0 = 0;                                            // the number of the entry's first segment
+  for (int e = 0; e < entry; ++e) g0 += max(1, (p.cu_seqlens[e + 1] - p.cu_seqlens[e] + p.seg_len - 1) / p.seg_len);
+  float S = (col == V) ? p.state_n[(size_t)slot * p.slot_stride + (size_t)h * D + kk]
+                       : p.state[(size_t)slot * p.slot_stride + (size_t)h * D * V + (size_t)kk * V + col];
+  const size_t seg_floats = (size_t)p.heads * D * p.v_tot;
+  const float* local = p.seg_local + ((size_t)g0 * p.heads + h) * D * p.v_tot + (size_t)kk * p.v_tot;
+  float* start = p.seg_start + ((size_t)(g0 + 1) * p.heads + h) * D * p.v_tot + (size_t)kk * p.v_tot + col;
+  float t_next = local[v_n], l_next = local[col];
+  for (int sg = 0; sg + 1 < n_seg; ++sg) {
+    const float t = t_next, l = l_next;
+    if (sg + 2 < n_seg) {                                // the next segment's numbers are under way
+      t_next = local[(size_t)(sg + 1) * seg_floats + v_n];
+      l_next = local[(size_t)(sg + 1) * seg_floats + col];
+    }
+    S = fmaf(t, S, l);
+    start[(size_t)sg * seg_floats] = S;
+  }
+}
+
+// With the removal term T_s is a [D][D] matrix.  One block per (entry, head, 32 columns); a thread keeps the rows
+// tid / 32, tid / 32 + 4, ... of its column.  Per segment the matrix comes into shared memory once (all threads, 16
+// bytes a load) beside the block's columns, and a row's product reads four of its numbers at a time.
+constexpr int COMBINE_ROWS = 64;     // rows a thread: keys up to 256
+__global__ void __launch_bounds__(128) scan_combine_kernel(const ScanParams p) {
+  extern __shared__ __align__(16) float csm[];           // cols [D][32], local [D][32], T [D][DP], DP = D rounded up to 4, plus 4
+  pdl_trigger();
+  pdl_wait();
+  const int entry = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int lane = tid & 31, col = blockIdx.z * 32 + lane, r0 = tid >> 5;
+  const int D = p.D, V = p.V;
+  const int DP = ((D + 3) & ~3) + 4;
+  float* cols = csm;
+  float* Ls = csm + (size_t)D * 32;
+  float* Ts = csm + (size_t)D * 64;
+  const int len = p.cu_seqlens[entry + 1] - p.cu_seqlens[entry];
+  const int n_seg = max(1, (len + p.seg_len - 1) / p.seg_len);
+  if (n_seg < 2) return;
+  const int slot = p.slots[entry];
+  if (slot < 0 || slot >= p.n_slots) return;             // the scan reports it
+  int g0 = 0;
+  for (int e = 0; e < entry; ++e) g0 += max(1, (p.cu_seqlens[e + 1] - p.cu_seqlens[e] + p.seg_len - 1) / p.seg_len);
+  const bool live = col < V;
+  const float* S_g = p.state + (size_t)slot * p.slot_stride + (size_t)h * D * V + col;
+  float S[COMBINE_ROWS];
+#pragma unroll
+  for (int i = 0; i < COMBINE_ROWS; ++i) {
+    const int kk = r0 + 4 * i;
+    S[i] = (live && kk < D) ? S_g[(size_t)kk * V] : 0.f;
+  }
+  for (int i = tid; i < D * DP; i += 128) Ts[i] = 0.f;   // the padding stays zero
+  for (int sg = 0; sg + 1 < n_seg; ++sg) {
+    const size_t base = ((size_t)(g0 + sg) * p.heads + h) * D * p.v_tot;
+    const float* local = p.seg_local + base;
+    __syncthreads();                                     // the round before has read the columns and the matrix
+#pragma unroll
+    for (int i = 0; i < COMBINE_ROWS; ++i) {
+      const int kk = r0 + 4 * i;
+      if (kk < D) cols[kk * 32 + lane] = S[i];
+    }
+    // the segment's matrix and the block's columns of its local result come in as asynchronous copies: no load waits
+    // for another
+    for (int i = tid; i < D * D; i += 128) {
+      const int kk = i / D, j = i - kk * D;
+      cp_async_4(Ts + kk * DP + j, local + (size_t)kk * p.v_tot + V + j);
+    }
+    if (live)
+      for (int kk = r0; kk < D; kk += 4) cp_async_4(Ls + kk * 32 + lane, local + (size_t)kk * p.v_tot + col);
+    cp_async_commit();
+    cp_async_wait_all();
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < COMBINE_ROWS; ++i) {
+      const int kk = r0 + 4 * i;
+      if (kk < D) {
+        const float* trow = Ts + kk * DP;
+        float a0 = live ? Ls[kk * 32 + lane] : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int j = 0; j < D; j += 4) {                 // past D the matrix's padding is zero and the columns are finite
+          const float4 t4 = *reinterpret_cast<const float4*>(trow + j);
+          a0 = fmaf(t4.x, cols[j * 32 + lane], a0);
+          if (j + 1 < D) a1 = fmaf(t4.y, cols[(j + 1) * 32 + lane], a1);
+          if (j + 2 < D) a2 = fmaf(t4.z, cols[(j + 2) * 32 + lane], a2);
+          if (j + 3 < D) a3 = fmaf(t4.w, cols[(j + 3) * 32 + lane], a3);
+        }
+        S[i] = (a0 + a1) + (a2 + a3);
+      }
+    }
+    float* start = p.seg_start + base + (size_t)D * p.v_tot * p.heads;      // the buffer of segment g0 + sg + 1
+#pragma unroll
+    for (int i = 0; i < COMBINE_ROWS; ++i) {
+      const int kk = r0 + 4 * i;
+      if (live && kk < D) start[(size_t)kk * p.v_tot + col] = S[i];
+    }
   }
 }
 
@@ -299,7 +476,28 @@ int launch_scan(const ScanParams& p, int entries, cudaStream_t stream) {
       }))
     return JV_ERR_UNSUPPORTED;
   const int cols = p.V + ((!REMOVAL && p.state_n != nullptr) ? 1 : 0);
-  return jv_launch(kern, dim3(entries, p.heads, (cols + SCAN_COLS - 1) / SCAN_COLS), dim3(SCAN_THREADS), smem, stream, p);
+  if (p.mode == 0)
+    return jv_launch(kern, dim3(entries, p.heads, (cols + SCAN_COLS - 1) / SCAN_COLS), dim3(SCAN_THREADS), smem, stream, p);
+  // in segments: `entries` is then the largest number of segments there can be
+  ScanParams q = p;
+  q.mode = 1;
+  int rc = jv_launch(kern, dim3(entries, p.heads, (p.v_tot + SCAN_COLS - 1) / SCAN_COLS), dim3(SCAN_THREADS), smem, stream, q);
+  if (rc != JV_OK) return rc;
+  if (REMOVAL) {
+    const size_t csmem = sizeof(float) * ((size_t)p.D * 64 + (size_t)p.D * (((p.D + 3) & ~3) + 4));
+    if (csmem > 200 * 1024) return JV_ERR_UNSUPPORTED;
+    static bool cdone[JV_MAX_DEVICES] = {};
+    if (!jv_once_per_device(cdone, [&] {
+          return cudaFuncSetAttribute(scan_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess;
+        }))
+      return JV_ERR_UNSUPPORTED;
+    rc = jv_launch(scan_combine_kernel, dim3(p.n_entries, p.heads, (cols + 31) / 32), dim3(128), csmem, stream, q);
+  } else {
+    rc = jv_launch(scan_combine_diag_kernel, dim3(p.n_entries, p.heads, (p.D * cols + 127) / 128), dim3(128), 0, stream, q);
+  }
+  if (rc != JV_OK) return rc;
+  q.mode = 2;
+  return jv_launch(kern, dim3(entries, p.heads, (cols + SCAN_COLS - 1) / SCAN_COLS), dim3(SCAN_THREADS), smem, stream, q);
 }
 
 template <bool REMOVAL, typename T>
@@ -379,13 +577,22 @@ JV_EXPORT int jv_memory_gates(const void* proj, int dtype, long long stride, int
 // The scan itself; `removal`: the packed rows hold (r, k, w, u, b), else (r, k, w).  v: rows of the projection.
 // state_n (or null; without removal only): [slots][heads * D], rows `slot_stride` apart, the state of one more column
 // whose value is 1 at every token; its outputs go to nq[(token * heads + head) * nq_stride].
+// seg_len > 0: entries longer than seg_len tokens run in segments of that many, side by side (see ScanParams): three
+// launches; seg_local and seg_start hold max_segments * heads * D * (V + (state_n ? 1 : 0) + (removal ? D : 1)) floats
+// each, and max_segments is at least the number of segments of all entries together.
 JV_EXPORT int jv_state_scan(const float* packed, int removal, const void* v, int dtype, long long v_stride, int v_off,
                             float* out, float* state, long long slot_stride, const int* cu_seqlens, const int* slots,
                             int n_slots, int entries, int heads, int D, int V, float* state_n, float* nq, int nq_stride,
-                            int* status, cudaStream_t stream) {
+                            int seg_len, int max_segments, float* seg_local, float* seg_start, int* status,
+                            cudaStream_t stream) {
   if (entries == 0) return JV_OK;
   if (state_n != nullptr && (removal || nq == nullptr)) return JV_ERR_UNSUPPORTED;
+  if (seg_len > 0 && (seg_local == nullptr || seg_start == nullptr || max_segments < entries || D > 4 * COMBINE_ROWS))
+    return JV_ERR_UNSUPPORTED;
   ScanParams p;
+  p.mode = seg_len > 0 ? 1 : 0; p.seg_len = seg_len; p.n_entries = entries; p.seg_local = seg_local; p.seg_start = seg_start;
+  p.v_tot = V + (state_n != nullptr ? 1 : 0) + (removal ? D : 1);
+  if (seg_len > 0) entries = max_segments;
   p.state_n = state_n; p.nq = nq; p.nq_stride = nq_stride;
   p.packed = packed; p.v = v; p.v_stride = v_stride; p.v_off = v_off; p.out = out; p.state = state;
   p.slot_stride = slot_stride; p.cu_seqlens = cu_seqlens; p.slots = slots; p.n_slots = n_slots; p.heads = heads;

@@ -1488,15 +1488,25 @@ def memory_gates(proj: torch.Tensor, q_off: int, k_off: int, i_off: int, f_off: 
     return packed, gates
 
 
+SCAN_SEGMENT = 64          # tokens of a segment when long entries are scanned in segments side by side
+SCAN_SEGMENT_MEAN = 32     # ... which happens when the entries of a step have this many tokens on average, at least
+
+
 def state_scan(packed: torch.Tensor, v: torch.Tensor, v_off: int, state: torch.Tensor, cu_seqlens: torch.Tensor,
                slots: torch.Tensor, n_entries: int, value_dim: int, state_n: torch.Tensor | None = None,
-               gates: torch.Tensor | None = None) -> torch.Tensor:
+               gates: torch.Tensor | None = None, segment: int | None = None) -> torch.Tensor:
     """S <- diag(w) S - b (u^T S) + k v^T and o = S^T r, token after token of every entry, for the per-head states
     `state` [slots, >= heads * dim * value_dim] float32 (a view of the state rows); `packed` [n, heads, 5 or 3, dim]
     holds (r, k, w, u, b) or, without the removal term, (r, k, w); the values are columns `v_off`.. of the rows of
     `v`.  Returns o [n, heads * value_dim] float32.  With `state_n` [slots, heads * dim] (a view of the same rows) the
     state has one more column whose value is 1 at every token (a normaliser n <- w n + k); its output n . r goes to
-    the fourth place of `gates` [n, heads, 4]."""
+    the fourth place of `gates` [n, heads, 4].
+
+    A step whose entries are long runs them in segments of `segment` tokens side by side (None: `SCAN_SEGMENT` when
+    the step has 4 segments' tokens and `SCAN_SEGMENT_MEAN` tokens an entry; 0: never): every segment first runs from
+    a zero state and records what it does to a state that comes in, the segments of an entry are chained, and every
+    segment runs again from its true start for the outputs.  The result differs from the token-by-token order by
+    32-bit rounding only."""
     _cuda(packed, "packed", torch.float32); _cuda(v, "v", contiguous=False)
     _cuda(state, "state", torch.float32, contiguous=False)
     _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(slots, "slots", torch.int32)
@@ -1512,12 +1522,25 @@ def state_scan(packed: torch.Tensor, v: torch.Tensor, v_off: int, state: torch.T
             raise KernelError("state_scan: the normaliser does not fit")
         nq = gates.data_ptr() + 3 * 4
     out = torch.empty((n, heads * value_dim), dtype=torch.float32, device=packed.device)
+    if segment is None:
+        # with the removal term a segment carries `dim` more columns and the chain is a matrix product a segment: at
+        # the sizes measured (32 heads of 64, 2,048 tokens) the three launches take longer than the one
+        segment = SCAN_SEGMENT if nv == 3 and n >= 4 * SCAN_SEGMENT and n >= SCAN_SEGMENT_MEAN * n_entries else 0
+    if nv == 5 and 4 * dim * (64 + (dim + 3) // 4 * 4 + 4) > 200 * 1024:
+        segment = 0          # the kernel that chains segments keeps a [dim][dim] transition in shared memory
+    max_segments, seg_local, seg_start = 0, None, None
+    if segment > 0:
+        max_segments = n // segment + n_entries
+        v_tot = value_dim + (1 if state_n is not None else 0) + (dim if nv == 5 else 1)
+        seg_local = torch.empty((2, max_segments, heads, dim, v_tot), dtype=torch.float32, device=packed.device)
+        seg_start = seg_local[1]
     f = _fn("recurrent", "jv_state_scan", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p,
                                            c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                           c_void_p, c_int, c_void_p, c_void_p])
+                                           c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(packed.data_ptr(), 1 if nv == 5 else 0, v.data_ptr(), _code(v, "v"), v.stride(0), v_off, out.data_ptr(),
              state.data_ptr(), state.stride(0), cu_seqlens.data_ptr(), slots.data_ptr(), state.shape[0], n_entries, heads,
-             dim, value_dim, _ptr(state_n), nq, 4, _status_ptr(packed.device), _stream()), "state_scan")
+             dim, value_dim, _ptr(state_n), nq, 4, int(segment), max_segments, _ptr(seg_local), _ptr(seg_start),
+             _status_ptr(packed.device), _stream()), "state_scan", launches=3 if segment > 0 else 1)
     return out
 
 

@@ -101,12 +101,14 @@ def entries_of(lengths, slots, n_slots):
     return cu, torch.tensor(slots, dtype=torch.int32).cuda()
 
 
+@pytest.mark.parametrize("segment", [0, 4, 7])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,V", [(2, 16, 16), (3, 20, 20), (1, 40, 40), (2, 64, 64), (1, 128, 128), (2, 7, 7), (1, 200, 200)])
-def test_delta_rule_alone(H, D, V, dtype):
+def test_delta_rule_alone(H, D, V, dtype, segment):
     """The prepare kernel and the scan with the removal term: three entries of unequal length (one of a single
     token) whose states start from random matrices in slots given out of order; a second call carries on from what
-    the first left, token by token, and an unused slot stays as it was."""
+    the first left, token by token, and an unused slot stays as it was.  `segment` > 0: the entries run in segments
+    of so many tokens side by side (23 tokens: whole segments and a rest; 9: one token more than two of 4)."""
     from jax_vllm_b200 import ops
     g = torch.Generator().manual_seed(H * D)
     lengths, slots, n_slots = [23, 1, 9], [3, 0, 4], 6
@@ -121,7 +123,7 @@ def test_delta_rule_alone(H, D, V, dtype):
     state = state0.clone().cuda()
     cu, sl = entries_of(lengths, slots, n_slots)
     packed = ops.delta_prepare(proj.cuda(), r_off, k_off, a_off, zw.cuda(), a_bias.cuda(), w_bias.cuda(), H, D)
-    o = ops.state_scan(packed, vrow.cuda(), 3, state, cu, sl, len(lengths), V)
+    o = ops.state_scan(packed, vrow.cuda(), 3, state, cu, sl, len(lengths), V, segment=segment)
     ops.check_status()
     p64 = proj.double()
     r, k = p64[:, r_off:r_off + H * D].view(n, H, D), p64[:, k_off:k_off + H * D].view(n, H, D)
@@ -150,10 +152,11 @@ def test_delta_rule_alone(H, D, V, dtype):
         assert (o2[row].cpu().double().view(1, H, V) - want).abs().max() < tol * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("segment", [0, 5, 8])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,V,cap", [(2, 8, 24, 15.0), (3, 20, 12, 8.0), (1, 36, 28, 4.0), (2, 128, 64, 15.0),
-                                       (1, 12, 6, 30.0), (1, 256, 40, 15.0), (4, 32, 32, 2.0)])
-def test_matrix_memory_alone(H, D, V, cap, dtype):
+                                       (1, 12, 6, 30.0), (1, 256, 40, 15.0), (4, 32, 32, 2.0), (1, 16, 31, 6.0)])
+def test_matrix_memory_alone(H, D, V, cap, dtype, segment):
     """The gate scan (normaliser and running maximum) and the matrix scan: entries of unequal length from states that
     are zero (a fresh request: the maximum starts at 0) or carried, gates pushed to both sides of their cap."""
     from jax_vllm_b200 import ops
@@ -176,7 +179,7 @@ def test_matrix_memory_alone(H, D, V, cap, dtype):
     packed, gates = ops.memory_gates(proj.cuda(), q_off, k_off, i_off, f_off, i_bias.cuda(), f_bias.cuda(), cap, D ** -0.5,
                                      state[:, mats + H * D:], cu, sl, len(lengths), H, D)
     o = ops.state_scan(packed, proj.cuda(), v_off, state, cu, sl, len(lengths), V, state_n=state[:, mats:mats + H * D],
-                       gates=gates)
+                       gates=gates, segment=segment)
     ops.check_status()
     # the scan leaves n . q and the running maximum in `gates`; the division by max(|n . q|, exp(-m)) + 1e-6 belongs
     # to the kernel that norms the heads (checked with it below) and is done here by hand
@@ -525,11 +528,11 @@ def test_the_bias_tables_edges_the_sink_and_the_temperature_show(dtype, tmp_path
 def long_memory_model(kind, others):
     """One layer whose state forgets almost nothing (decays of nearly one and no removal for the delta rule, a forget
     gate of nearly one for the matrix memory, whose attention side is switched off by its output weight), without
-    position vectors, in which the last token (2) reads what token 1 wrote wherever that stood: token 1's embedding
-    is the first unit vector, token 2's is minus that, no other token has a first component (and the norm's offset
-    is zero, so that none gets one); in every head the first column of the key matrix is a vector b to which the
-    other columns, times `others`, are made orthogonal, and the first column of the query matrix is minus three times b.
-    What the other tokens write is read only through rounding; the smaller it is, the sharper the 32-bit comparison."""
+    position vectors, in which the last token (2) reads what token 1 wrote wherever that stood.  Token 1's embedding
+    is the first unit vector, token 2's the second, no other token has either component (and the norm's offset is
+    zero, so that none gets one).  In every head the first column of the key matrix is a vector b to which the other
+    columns, times `others`, are made orthogonal, and the second column of the query matrix is three times b: token
+    1's key is b, every other key is orthogonal to it, and token 2's query reads along b only."""
     if kind == "delta":
         c = config(60, 32, [layer(delta(2, 16, rank=4), None)], eps=1e-6, softcap=40.0, max_positions=700)
         key, query, H, D = "l0.mix.k", "l0.mix.r", 2, 16
@@ -539,12 +542,13 @@ def long_memory_model(kind, others):
         key, query, H, D = "l0.mix.right.k", "l0.mix.right.q", 2, 16
     w = make_weights(c, seed=33)
     w["pos"] *= 0.0
-    w["embed"][:, 0] = 0.0
+    w["embed"][:, :2] = 0.0
     w["embed"][1] = 0.0
     w["embed"][1, 0] = 4.0
-    w["embed"][2] = -w["embed"][1]
+    w["embed"][2] = 0.0
+    w["embed"][2, 1] = 4.0
     w["l0.norm1.b"][:] = 0.0
-    w["l0.norm1"][0] = 1.0
+    w["l0.norm1"][:2] = 1.0
     g = torch.Generator().manual_seed(34)
     wk = w[key].view(H, D, 32).clone()
     for blk in range(H):
@@ -554,7 +558,7 @@ def long_memory_model(kind, others):
         wk[blk][:, 1:] = others * (rest - b[:, None] * (b @ rest)[None, :])
         wk[blk][:, 0] = b
     w[key] = wk.reshape(H * D, 32).contiguous()
-    w[query][:, 0] = -3.0 * w[key][:, 0]
+    w[query][:, 1] = 3.0 * w[key][:, 0]
     if kind == "delta":
         w["l0.mix.w0"][:] = -14.0
         w["l0.mix.w2"] *= 0.0
@@ -575,7 +579,7 @@ def test_a_token_far_back_in_the_state(kind, far, dtype, tmp_path):
     """Token 1 stands at position `far` only among 500 tokens and the last token reads its trace in the state: taking it
     away changes the plain implementation's last logits greatly, and the engine's equal the plain ones whole, in
     portions and decoded (a state that is lost, restarted or overwritten at a portion's edge loses that token)."""
-    c, w = long_memory_model(kind, 0.05 if dtype == "float32" else 1.0)
+    c, w = long_memory_model(kind, 0.05)
     w64 = stored(w)
     tokens = [3 + (i * 7) % 11 for i in range(500)]
     tokens[far], tokens[-1] = 1, 2
@@ -583,7 +587,7 @@ def test_a_token_far_back_in_the_state(kind, far, dtype, tmp_path):
     without = list(tokens)
     without[far] = 4
     gone = npl.forward(c, w64, without).to(torch.float32)
-    assert (want[-1] - gone[-1]).abs().max() > (0.015 if dtype == "float32" else 0.15)      # 150 times, twice the limit
+    assert (want[-1] - gone[-1]).abs().max() > 0.3
     for sizes, tail in ((None, 0), ((100, 3, 2), 0), (None, 9)):
         steps, out = special(tmp_path, c, w, tokens, dtype, sizes=sizes, tail=tail)
         compare(steps, out, 60, {"r": want}, dtype, case=f"nufapel far token in the state ({kind})")
