@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(128) scan_combine_kernel(const ScanParams p) {
   for (int sg = 0; sg + 1 < n_seg; ++sg) {
     const size_t base = ((size_t)(g0 + sg) * p.heads + h) * D * p.v_tot;
     const float* local = p.seg_local + base;
-    __syncthreads();                                     // the round before has read the columns and the matrix
+    __syncthreads();                                     // the segment before has read the columns and the matrix
 #pragma unroll
     for (int i = 0; i < COMBINE_ROWS; ++i) {
       const int kk = r0 + 4 * i;
