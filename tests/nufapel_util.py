@@ -68,8 +68,14 @@ NC = config(320, 128, [layer(pair(8, 2, 64, 64, 2, 128, 64, bias_max=200, bucket
                        layer(pair(4, 4, 32, 32, 4, 32, 32, bias_max=64, buckets=16), None)], eps=1e-5, loop=(0, 2, 3))
 # one layer, one head everywhere, a loop of one pass
 ND = config(90, 40, [layer(pair(1, 1, 16, 24, 1, 12, 6, bias_max=9, buckets=4), dense(8))], eps=1e-5, loop=(0, 1, 1))
-CONFIGS = {"na": NA, "nb": NB, "nc": NC, "nd": ND}
-PAGE = {"na": 16, "nb": 8, "nc": 16, "nd": 4}
+# attention heads of 128 with values of 128 (prompt tiles of 64 tokens on the tcgen05 kernel in bfloat16), a memory with
+# keys of 256, a delta rule with heads of 200 (not a multiple of 16), a table with an odd number of heads' columns
+NE = config(150, 96, [layer(pair(4, 2, 128, 128, 1, 256, 16, bias_max=50, buckets=10), dense(64)),
+                      layer(delta(1, 200, rank=3), None),
+                      layer(pair(3, 3, 128, 128, 2, 16, 48, bias_max=300, buckets=20, cap=10.0), dense(40))],
+            eps=1e-5, loop=(0, 1, 2), softcap=25.0)
+CONFIGS = {"na": NA, "nb": NB, "nc": NC, "nd": ND, "ne": NE}
+PAGE = {"na": 16, "nb": 8, "nc": 16, "nd": 4, "ne": 32}
 
 
 def tensor_shapes(c: dict) -> dict:

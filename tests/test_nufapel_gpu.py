@@ -23,7 +23,8 @@ from tests.util import collect, portions, prefix_then_single, random_tokens, who
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"na": [70, 45, 100, 33, 52], "nb": [90, 38, 64, 51, 27], "nc": [200, 70, 150, 40, 66], "nd": [61, 40, 83, 35, 20]}
+LENGTHS = {"na": [70, 45, 100, 33, 52], "nb": [90, 38, 64, 51, 27], "nc": [200, 70, 150, 40, 66], "nd": [61, 40, 83, 35, 20],
+           "ne": [170, 60, 100, 37, 45]}
 CLOSE_CALL = 0.02      # a difference of router scores below which bfloat16 may choose another expert
 EXCUSED = 0.25         # share of the positions that may differ for that reason
 
