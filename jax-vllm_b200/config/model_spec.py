@@ -252,6 +252,7 @@ class ModelSpec:
     # ((place, row), ...)), or None
     pass_vectors: Optional[tuple] = None
     logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap)
+    unused_tensors: tuple = ()    # names that a folder may hold without the model reading them
 
     def run_order(self) -> tuple:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))

@@ -201,10 +201,16 @@ class NufapelConfig:
                                     ffn_norm=None if ff is None else NormSpec(W, eps, "norm2", kind="dyt"),
                                     kind="pre_norm", residual_gates=("rg1", "rg2")))
         order, starts = self.run_order()
+        # a layer without a feed-forward reads no second norm and no second gate, and a model without a loop no pass
+        # vectors: a folder that holds them all the same is taken as it is
+        unused = [f"l{i}.{name}" for i, layer in enumerate(layers) if layer.feed_forward is None
+                  for name in ("norm2", "norm2.b", "norm2.alpha", "rg2", "rg2.b")]
+        if not starts:
+            unused.append("loop.step")
         spec = ModelSpec(architecture=ARCHITECTURE, vocab_size=self.vocab, hidden_size=W, layers=tuple(layers),
                          final_norm=NormSpec(W, eps, "final.norm", kind="dyt"), embedding_name="embed",
                          lm_head_name="head", schedule=order, max_position=self.max_positions,
                          position_table_name="pos", pass_vectors=("loop.step", starts) if starts else None,
-                         logit_softcap=self.logit_softcap)
+                         logit_softcap=self.logit_softcap, unused_tensors=tuple(unused))
         spec.validate()
         return spec

@@ -56,7 +56,7 @@ class Model(Part):
     def optional_tensors(self):
         """Names that may be in the folder without being used (the output matrix of a tied
         model is ignored, jllm/model/weights.py:142-146)."""
-        return {"lm_head.weight"} if self.spec.lm_head_name is None else set()
+        return ({"lm_head.weight"} if self.spec.lm_head_name is None else set()) | set(self.spec.unused_tensors)
 
     def bind(self, tensors):
         s = self.spec

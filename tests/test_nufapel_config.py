@@ -81,6 +81,20 @@ def test_what_the_design_does_not_have_is_refused():
     broken(lambda c: c.pop("norm"))
 
 
+def test_a_folder_may_hold_the_second_norm_of_a_layer_without_a_feed_forward():
+    from jax_vllm_b200.weights import loader
+    c = CONFIGS["nb"]                                     # its first layer has no feed-forward, and it has no loop
+    model = Model(registry.config_from_dict(config_json(c)).to_spec(), BuildContext(dtype=torch.float32, device=torch.device("cpu")))
+    index = {name: (None, [16 if d == -1 else d for d in spec.shape], "BF16") for name, spec in model.tensor_specs().items()}
+    W = c["width"]
+    index.update({"l0.norm2": (None, [W], "BF16"), "l0.rg2": (None, [W, W], "BF16"), "loop.step": (None, [1, W], "BF16")})
+    loader.check("folder", index, model.tensor_specs(), model.optional_tensors())
+    index["l1.rg3"] = (None, [W, W], "BF16")
+    with pytest.raises(loader.WeightError) as err:
+        loader.check("folder", index, model.tensor_specs(), model.optional_tensors())
+    assert err.value.unexpected == ["l1.rg3"]
+
+
 def test_distance_buckets_of_the_product_and_of_the_plain_implementation():
     for B, far in ((8, 30), (16, 120), (4, 5), (32, 1024), (6, 17), (12, 100)):
         table = distance_buckets(B, far)
