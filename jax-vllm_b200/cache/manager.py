@@ -4,8 +4,8 @@ Layers are put into groups by what they need: all layers with the same `PagedKVN
 (kv heads, head size, window) share one group, with one pool of pages and one block
 table per request; a page id of a group addresses the same page in every layer of the
 group.  Layers with a `FixedStateNeed` get a row per state slot instead.  Pages are given
-back when a request ends, when it is preempted, and - in a group with a window - as soon
-as every position of a page lies before the window of the next query.
+back when a request ends, when it is preempted, and - in a group with a window or with
+chunks - as soon as every position of a page lies before what the next query can see.
 
 Prefix reuse (jllm/engine/cache.py:20-57): full pages are hashed in a chain over the
 tokens; a new request takes the longest run of pages whose hashes are known, in every
@@ -180,13 +180,13 @@ class CacheManager:
             for i in range((len(prompt) - 1) // P):       # always leaves >= 1 token to compute
                 h = chain_hash(parent, prompt[i * P:(i + 1) * P])
                 pages = [grp.pool.lookup(h) for grp in self.groups]
-                if any(p is None and grp.need.window is None for p, grp in zip(pages, self.groups)):
+                if any(p is None and grp.need.window is None and grp.need.chunk is None for p, grp in zip(pages, self.groups)):
                     break
                 hashes.append(h)
                 found.append(pages)
                 parent = h
             n = len(hashes)                               # pages known from the start where there is no window
-            windowed = [g for g, grp in enumerate(self.groups) if grp.need.window is not None]
+            windowed = [g for g, grp in enumerate(self.groups) if grp.need.window is not None or grp.need.chunk is not None]
             while n > 0 and not all(found[i][g] is not None for g in windowed
                                     for i in range(self._first_page_needed(g, n * P), n)):
                 n -= 1
@@ -206,9 +206,15 @@ class CacheManager:
 
     def _first_page_needed(self, g: int, num_tokens: int) -> int:
         """The first logical page of group g that a query at position >= num_tokens can still see: it sees keys at
-        positions > num_tokens - window, and all keys in a group without a window."""
-        w = self.groups[g].need.window
-        return 0 if w is None else max(0, num_tokens - w + 1) // self.page_size
+        positions > num_tokens - window, or from the start of the chunk that holds position num_tokens on, and all
+        keys in a group with neither."""
+        need = self.groups[g].need
+        first = 0
+        if need.window is not None:
+            first = max(first, num_tokens - need.window + 1)
+        if need.chunk is not None:
+            first = max(first, num_tokens - num_tokens % need.chunk)
+        return first // self.page_size
 
     def pages_needed(self, rc: RequestCache, new_len: int) -> list:
         """Pages each group must still allocate so that positions < new_len have a page."""
@@ -250,7 +256,7 @@ class CacheManager:
                     grp.pool.register(rc.tables[g][i], h)
                 rc.hashes.append(h)
         for g, grp in enumerate(self.groups):
-            if grp.need.window is None:
+            if grp.need.window is None and grp.need.chunk is None:
                 continue
             upto = self._first_page_needed(g, rc.num_tokens)
             for i in range(rc.freed_upto[g], min(upto, len(rc.tables[g]))):

@@ -21,6 +21,7 @@ class NormSpec:
     eps: float
     name: str                      # tensor name of the weight, relative to the owner's prefix
     kind: str = "rmsnorm"          # "rmsnorm", or "dyt": tanh(alpha * x) * weight + bias (`<name>.alpha`, `<name>.b`)
+    offset: float = 0.0            # rmsnorm: the stored weight plus this number multiplies (1.0: a weight stored around zero)
 
 
 @dataclass(frozen=True)
@@ -29,6 +30,8 @@ class RopeSpec:
     theta: float
     kind: str = "rope"
     exact_table: bool = False      # the frequency table is formed in 64-bit and rounded once (else in 32-bit)
+    scaling_factor: float = 1.0    # linear scaling: every frequency is divided by this number
+    layout: str = "halves"         # pairs of the rotation: "halves" (i with i + dim/2) or "interleaved" (2i with 2i + 1)
 
 
 @dataclass(frozen=True)
@@ -91,11 +94,40 @@ class GeneralAttentionSpec:
     # row count, the distance from which the last bucket serves); see parts.general_attention.distance_buckets
     distance_bias: Optional[tuple] = None
     sink: bool = False                      # exp(a learned number per head) counts once in the softmax's denominator
+    # RMSNorm of every query and key head with ONE weight vector of the key size that all heads share (the norms'
+    # names serve both kinds; a layer has the whole-projection norm or this one)
+    head_norm_eps: Optional[float] = None
+    value_norm_eps: Optional[float] = None  # every value head divided by its root mean square (no weight); cached so
+    # values rotated by their own position over their whole size (frequencies theta^(-2m/value_dim), never scaled, the
+    # position encoding's theta and layout), cached so; every head's output turned back by the query's position
+    rotate_values: bool = False
+    window: Optional[int] = None            # a query sees its own position and the window - 1 before it
+    chunk: Optional[int] = None             # a query sees the earlier positions of its chunk, chunks counted from 0
     prefix: str = "mix"
     # tensor names below the prefix: queries, keys, values, gate, output, whole-projection norms, score bias,
     # temperature, distance bias, sink
     names: tuple = ("q", "k", "v", "g", "o", "q.norm", "k.norm", "pb", "temp", "rel", "sink")
     kind: str = "general_attention"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A Mamba-2 mixer (state-space duality): the input product gives [z | x | B | C | dt]; x, B and C pass a short
+    causal convolution with a bias and silu; per head a state S [state, value_dim] with S <- exp(-exp(A_log) dt) S +
+    dt B x^T, y = S^T C + D x, dt = softplus(dt + dt_bias); B and C are shared by the heads of a group; y times
+    silu(z), RMS-normed in `norm_groups` equal parts, times a weight, then the output product."""
+    hidden_size: int
+    num_heads: int
+    value_dim: int
+    state_dim: int
+    groups: int
+    norm_groups: int
+    conv_taps: int
+    norm_eps: float
+    prefix: str = "mix"
+    # input product, convolution and its bias, step bias, log of the decay rate, skip, norm weight, output product
+    names: tuple = ("in", "conv", "conv.b", "dt_bias", "A_log", "D", "norm", "o")
+    kind: str = "state_space"
 
 
 @dataclass(frozen=True)
@@ -175,6 +207,13 @@ class LatentAttentionSpec:
     # tensor names below the prefix: queries, down-projection (latent | key part), latent norm, key and value
     # up-projections, gate, output
     names: tuple = ("q", "dkv", "dkv.norm", "uk", "uv", "g", "o")
+    # queries through a latent of their own: c_q = RMSNorm(W_dq x) (eps = latent_norm_eps), q = W_uq c_q; the three
+    # tensors' names below the prefix.  None: q = W_q x
+    query_latent_dim: Optional[int] = None
+    query_names: tuple = ("dq", "dq.norm", "uq")
+    window: Optional[int] = None   # a query sees its own position and the window - 1 before it
+    sink: Optional[str] = None     # tensor name below the prefix of a number per head: exp(sink) counts once in the
+                                   # softmax's denominator, with no key and no value
     kind: str = "latent_attention"
 
 
@@ -230,6 +269,10 @@ class LayerSpec:
     # element with x the sublayer's input (`<name>` [hidden, hidden], `<name>.b`), or None
     residual_gates: Optional[tuple] = None
     token_input: Any = None        # a further branch fed by the token id (TokenInputSpec), or None
+    # pre_norm: what each sublayer reads, u, is replaced by u + conv(u), a short causal convolution over time on each
+    # channel: (taps, (tensor name for the mixer's input, for the feed-forward's)), tensors [hidden, taps] below the
+    # prefix; the last taps - 1 inputs of a sequence are part of its state.  None: no convolution
+    input_conv: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -252,6 +295,7 @@ class ModelSpec:
     # ((place, row), ...)), or None
     pass_vectors: Optional[tuple] = None
     logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap)
+    logit_scale: Optional[float] = None     # logits <- logits * scale
     unused_tensors: tuple = ()    # names that a folder may hold without the model reading them
 
     def run_order(self) -> tuple:

@@ -233,6 +233,22 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
   for (; idx < total; idx += stride) x[idx] = cap * tanhf(x[idx] / cap);
 }
 
+__global__ void scale_kernel(float* __restrict__ x, size_t total, float factor) {
+  pdl_trigger();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) x[idx] *= factor;
+}
+
+// x[i] *= factor, in place (the logits of a model with a logit scale).
+JV_EXPORT int jv_scale(float* x, long long total, float factor, cudaStream_t stream) {
+  if (total <= 0) return JV_OK;
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  return jv_launch(scale_kernel, dim3((int)blocks), dim3(256), 0, stream, x, (size_t)total, factor);
+}
+
 JV_EXPORT int jv_softcap(float* x, long long total, float cap, cudaStream_t stream) {
   if (total <= 0) return JV_OK;
   if (!(cap > 0.f)) return JV_ERR_UNSUPPORTED;

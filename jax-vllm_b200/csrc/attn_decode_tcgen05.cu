@@ -796,7 +796,7 @@ int launch(int n_blocks, cudaStream_t stream, const CUtensorMap& q_map, const CU
 // 1 if this kernel takes the case (else the caller uses the mma.sync kernel).
 JV_EXPORT int jv_attn_decode_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size, int window,
                                               int n_work) {
-  if (head_dim != 128 || window > 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
+  if (head_dim != 128 || window != 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
   if (n_q_heads / n_kv_heads > NH || n_work > MAX_WORK) return 0;
   return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }

@@ -232,7 +232,7 @@ __device__ __forceinline__ void weights_tile(float (&s)[NB][4], float (&o)[VD / 
         if (MASK) {
           const int key = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
           const int pos = (i < 2) ? pos0 : pos1;
-          vis = key < j_end && key <= pos && (window <= 0 || key > pos - window);
+          vis = key < j_end && key <= pos && key >= first_visible(pos, window);
         }
         const float x = s[nb][i] + ((i < 2) ? bias0 : bias1);
         s[nb][i] = vis ? fast_rcp(1.f + fast_exp2(-x * LOG2E)) : 0.f;
@@ -247,7 +247,7 @@ __device__ __forceinline__ void weights_tile(float (&s)[NB][4], float (&o)[VD / 
       if (MASK) {
         const int key = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
         const int pos = (i < 2) ? pos0 : pos1;
-        const bool vis = key < j_end && key <= pos && (window <= 0 || key > pos - window);
+        const bool vis = key < j_end && key <= pos && key >= first_visible(pos, window);
         if (!vis) s[nb][i] = -INFINITY;
       }
       mx[i >> 1] = fmaxf(mx[i >> 1], s[nb][i]);
@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_general_kernel(const Par
   const int tokens_here = min(p.tokens_per_tile, q_len - q_off);
   if (tokens_here <= 0) return;
   const int pos_first = ctx + q_off;
-  const int j_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  const int j_lo = first_visible(pos_first, p.window);
   const int j_hi = pos_first + tokens_here;   // exclusive
 
   // ---- queries of the tile (unused rows zero)
@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_general_kernel(const Par
       qk_tile<KD, BN / 8>(s, qs + warp * 16 * SK, ks + buf * BN * SK, lane);
       // the test is needed only where the tile reaches past the first row's position, past the end,
       // or a window cuts into it
-      if (key0 + BN - 1 > warp_first || key0 + BN > j_hi || p.window > 0)
+      if (key0 + BN - 1 > warp_first || key0 + BN > j_hi || p.window != 0)
         weights_tile<BN / 8, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, scale[0], scale[1], dist[0], dist[1], p.n_dist, p.score_cap, sigmoid,
                                    bias[0], bias[1], lane);
       else
@@ -458,7 +458,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_general_kernel(const Para
   const int G = p.n_q_heads / p.n_kv_heads;
   const int HPT = p.heads_per_tile;
   const int pos_q = p.start_pos[entry];
-  const int vis_lo = p.window > 0 ? max(0, pos_q - p.window + 1) : 0;   // visible keys: [vis_lo, pos_q]
+  const int vis_lo = first_visible(pos_q, p.window);   // visible keys: [vis_lo, pos_q]
   const int j_lo = max(vis_lo, (int)blockIdx.z * p.split_size);
   const int j_hi = min(pos_q + 1, ((int)blockIdx.z + 1) * p.split_size);
   if (j_lo >= j_hi) return;

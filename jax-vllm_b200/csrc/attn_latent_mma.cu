@@ -30,6 +30,8 @@ struct LatentParams {
   const int* cu_seqlens; const int* start_pos; const int* work;
   int n_heads, dk, dv, page_size, num_pages;
   float scale;
+  int window;                    // the mask as one number (common.cuh, first_visible)
+  const float* sink;             // [n_heads] or null: exp(sink) counts once in the softmax's denominator, with no value
   int tokens_per_tile, heads_per_tile, split_size, n_splits;
   int qstride_s, kstride_s;      // shared-memory row strides (elements) of the query tile and of a key chunk
   int* status;
@@ -79,9 +81,9 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
   const int ctx = p.start_pos[entry];
   const int tokens_here = min(p.tokens_per_tile, q_len - q_off);
   if (tokens_here <= 0) return;
-  int j_lo = 0, j_hi = ctx + q_off + tokens_here;      // keys [j_lo, j_hi)
+  int j_lo = first_visible(ctx + q_off, p.window), j_hi = ctx + q_off + tokens_here;      // keys [j_lo, j_hi)
   if (SPLIT) {
-    j_lo = blockIdx.z * p.split_size;
+    j_lo = max(j_lo, (int)blockIdx.z * p.split_size);
     j_hi = min(j_hi, (blockIdx.z + 1) * p.split_size);
     if (j_lo >= j_hi) return;
   }
@@ -216,7 +218,7 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
       for (int k = 0; k < 4; ++k) {
         const int j = j0 + i * 8 + (lane & 3) * 2 + (k & 1);
         const int pos = (k < 2) ? pos0 : pos1;
-        const bool vis = pos >= 0 && j < j_hi && j <= pos;
+        const bool vis = pos >= 0 && j < j_hi && j <= pos && j >= first_visible(pos, p.window);
         s[i][k] = vis ? s[i][k] * scale_log2 : -INFINITY;
       }
       mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
@@ -271,13 +273,20 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     if (row_pos_s[m] < 0) continue;
     const int t = m / p.heads_per_tile, head = hg * p.heads_per_tile + m % p.heads_per_tile;
     const size_t token = (size_t)(q_begin + q_off + t);
-    const float l = half ? l1 : l0, mm = half ? m1 : m0;
+    float l = half ? l1 : l0;
+    const float mm = half ? m1 : m0;
+    float keep = 1.f;
+    if (!SPLIT && p.sink != nullptr) {     // the sink joins the denominator, both brought to the larger of the two maxima
+      const float sk = p.sink[head] * 1.4426950408889634f, mx = fmaxf(mm, sk);
+      keep = (mm == -INFINITY) ? 0.f : exp2f(mm - mx);
+      l = l * keep + exp2f(sk - mx);
+    }
     size_t slot = 0;
     if (SPLIT) {
       slot = ((size_t)item * p.n_heads + head) * p.n_splits + blockIdx.z;
       if (dw == 0 && (lane & 3) == 0) { p.part_ml[slot * 2] = mm; p.part_ml[slot * 2 + 1] = l; }
     }
-    const float inv = 1.f / l;
+    const float inv = keep / l;
 #pragma unroll
     for (int i = 0; i < DVW / 8; ++i) {
       const int d = dw * DVW + i * 8 + (lane & 3) * 2;
@@ -310,18 +319,21 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const LatentParams 
     s_last = p.n_splits - 1;
   }
   const size_t base = ((size_t)x * p.n_heads + head) * p.n_splits;
+  const int s_first = first_visible(pos, p.window) / p.split_size;      // splits before it hold no visible key
+  const float sk = p.sink != nullptr ? p.sink[head] * 1.4426950408889634f : -INFINITY;
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
-    float m_all = -INFINITY;
-    for (int s = lane; s <= s_last; s += 32) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
+    float m_all = sk;
+    for (int s = s_first + lane; s <= s_last; s += 32) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
     m_all = warp_max(m_all);
     float l = 0.f;
-    for (int s = lane; s <= s_last; s += 32) {
+    for (int s = s_first + lane; s <= s_last; s += 32) {
       const float w = exp2f(p.part_ml[(base + s) * 2] - m_all);
       w_s[s] = w;
       l += w * p.part_ml[(base + s) * 2 + 1];
     }
     l = warp_sum(l);
+    if (p.sink != nullptr) l += exp2f(sk - m_all);      // one more part, with no value
     if (lane == 0) l_s = l;
   }
   __syncthreads();
@@ -330,7 +342,7 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const LatentParams 
   __nv_bfloat16* dst = p.out + token * p.out_stride + (size_t)head * p.dv;
   for (int d = threadIdx.x; d < p.dv; d += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s <= s_last; ++s) o = fmaf(w_s[s], p.part_o[(base + s) * p.dv + d], o);
+    for (int s = s_first; s <= s_last; ++s) o = fmaf(w_s[s], p.part_o[(base + s) * p.dv + d], o);
     dst[d] = __float2bfloat16_rn(o * inv);
   }
 }
@@ -380,13 +392,13 @@ JV_EXPORT int jv_attn_latent_mma_supports(int dk, int dv) {
 
 // q: bfloat16 rows of q_stride elements (head h of token n at q[n*q_stride + h*dk]); out: [n, out_stride], head h at
 // h*dv; cache: [num_pages, page_size, dk] bfloat16; block_table, cu_seqlens, start_pos, work as for the other paged
-// attention kernels.  n_splits == 0: every work item attends to all its keys and writes `out`.  n_splits > 0: work
+// attention kernels; window: the mask (0: causal only); sink: [n_heads] floats or null.  n_splits == 0: every work item attends to all its keys and writes `out`.  n_splits > 0: work
 // items are single tokens; part_o [n_work*heads*n_splits*dv] and part_ml [n_work*heads*n_splits*2] floats are scratch.
 JV_EXPORT int jv_attn_latent_mma(const void* q, int q_stride, void* out, int out_stride, float* part_o, float* part_ml,
                                  const void* cache, const int* block_table, int table_width, const int* cu_seqlens,
                                  const int* start_pos, const int* work, int n_work, int n_heads, int dk, int dv,
-                                 int page_size, int num_pages, float scale, int split_size, int n_splits, int* status,
-                                 cudaStream_t stream) {
+                                 int page_size, int num_pages, float scale, int window, const float* sink, int split_size,
+                                 int n_splits, int* status, cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
   if (!jv_attn_latent_mma_supports(dk, dv) || n_heads < 1 || n_splits > COMBINE_MAX_SPLITS || (q_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)cache % 16))
     return JV_ERR_UNSUPPORTED;
@@ -394,7 +406,7 @@ JV_EXPORT int jv_attn_latent_mma(const void* q, int q_stride, void* out, int out
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
   p.part_o = part_o; p.part_ml = part_ml; p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table;
   p.table_width = table_width; p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_heads = n_heads;
-  p.dk = dk; p.dv = dv; p.page_size = page_size; p.num_pages = num_pages; p.scale = scale; p.status = status;
+  p.dk = dk; p.dv = dv; p.page_size = page_size; p.num_pages = num_pages; p.scale = scale; p.window = window; p.sink = sink; p.status = status;
   p.heads_per_tile = n_heads < BLOCK_M ? n_heads : BLOCK_M;
   p.tokens_per_tile = n_splits > 0 ? 1 : BLOCK_M / p.heads_per_tile;
   p.split_size = split_size > 0 ? split_size : 1;

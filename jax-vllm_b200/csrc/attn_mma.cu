@@ -196,7 +196,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NB][4], float (&o)[D / 8
       if (MASK) {
         const int key = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
         const int pos = (i < 2) ? pos0 : pos1;
-        const bool vis = key < j_end && key <= pos && (window <= 0 || key > pos - window);
+        const bool vis = key < j_end && key <= pos && key >= first_visible(pos, window);
         if (!vis) s[nb][i] = -INFINITY;
       }
       mx[i >> 1] = fmaxf(mx[i >> 1], s[nb][i]);
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
   const int tokens_here = min(p.tokens_per_tile, q_len - q_off);
   if (tokens_here <= 0) return;
   const int pos_first = ctx + q_off;
-  const int j_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  const int j_lo = first_visible(pos_first, p.window);
   const int j_hi = pos_first + tokens_here;   // exclusive
 
   // ---- queries of the tile (unused rows zero)
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_mma_kernel(const Params 
       qk_tile<D, BN / 8>(s, qs + warp * 16 * S, ks + buf * BN * S, lane);
       // the test is needed only where the tile reaches past the first row's position, past the end,
       // or a window cuts into it
-      if (key0 + BN - 1 > warp_first || key0 + BN > j_hi || p.window > 0)
+      if (key0 + BN - 1 > warp_first || key0 + BN > j_hi || p.window != 0)
         softmax_tile<D, BN / 8, true>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale_log2, lane);
       else
         softmax_tile<D, BN / 8, false>(s, o_acc, m, l, pos[0], pos[1], key0, j_hi, p.window, p.scale_log2, lane);
@@ -381,7 +381,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_mma_kernel(const Params p
   const int G = p.n_q_heads / p.n_kv_heads;
   const int HPT = p.heads_per_tile;
   const int pos_q = p.start_pos[entry];
-  const int vis_lo = p.window > 0 ? max(0, pos_q - p.window + 1) : 0;   // visible keys: [vis_lo, pos_q]
+  const int vis_lo = first_visible(pos_q, p.window);   // visible keys: [vis_lo, pos_q]
   const int j_lo = max(vis_lo, (int)blockIdx.z * p.split_size);
   const int j_hi = min(pos_q + 1, ((int)blockIdx.z + 1) * p.split_size);
   if (j_lo >= j_hi) return;

@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
 
   // visible key range of the tile
   const int pos_first = ctx + q_off, pos_last = ctx + q_off + tokens_here - 1;
-  int j_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  int j_lo = first_visible(pos_first, p.window);
   int j_hi = pos_last + 1;  // exclusive
   if (SPLIT) {
     j_lo = max(j_lo, blockIdx.z * p.split_size);
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
       for (int r = 0; r < 4; ++r) {
         const int m = warp * 4 + r;
         const int pos = row_pos[m];
-        const bool vis = pos >= 0 && j < j_hi && j <= pos && (p.window <= 0 || j > pos - p.window);
+        const bool vis = pos >= 0 && j < j_hi && j <= pos && j >= first_visible(pos, p.window);
         float sc = s[r] * p.scale;
         if (p.head_scale != nullptr || p.dist_bias != nullptr) {
           const int hq = min(hg * p.heads_per_tile + m % p.heads_per_tile, G - 1) + kv_head * G;
@@ -239,7 +239,7 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   const int entry = p.work[2 * x];
   const int D = p.v_dim;
   const int pos = p.start_pos[entry];
-  const int j_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int j_lo = first_visible(pos, p.window);
   const int j_hi = pos + 1;
   const int s_first = j_lo / p.split_size;
   int s_last = (j_hi - 1) / p.split_size;  // inclusive

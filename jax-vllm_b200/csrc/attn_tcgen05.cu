@@ -718,7 +718,7 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 
 // 1 if this kernel takes the case (else the caller uses the mma.sync kernel).
 JV_EXPORT int jv_attn_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size, int window) {
-  if (head_dim != 128 || window > 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
+  if (head_dim != 128 || window != 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
   const int G = n_q_heads / n_kv_heads;
   if (G > 16) return 0;
   return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;

@@ -69,6 +69,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return t;
 }
 
+// The first key position that a query at `pos` sees under a mask given as one number: mask > 0, a window of the last
+// `mask` positions (the query's own included); mask < 0, the chunk of -mask positions that holds the query, chunks
+// counted from position 0 of the sequence; 0, every earlier position.  Keys after the query are never visible.
+__device__ __forceinline__ int first_visible(int pos, int mask) {
+  return mask > 0 ? max(0, pos - mask + 1) : mask < 0 ? pos - pos % (-mask) : 0;
+}
+
 // Programmatic dependent launch.  A kernel launched through jv_launch may be made resident while the
 // kernel before it in the stream is still finishing; whatever it does before `pdl_wait()` (index
 // arithmetic, prefetching weights that no kernel writes) overlaps that kernel's tail, and everything

@@ -8,8 +8,8 @@
 //     the rotated part from the product row, q_latent (the head's plain query part times W_uk, made by a batched
 //     product before this kernel) copied from [heads, n, latent_dim] if it is given there (else the product has
 //     written it in place already).
-// Rotation: element i of the part is paired with i + rot_dim/2; angle = position * inv_freq[i], cos and sin in
-// 32-bit.  A layer that reads another layer's cache passes no cache and only gets its queries made.
+// Rotation: element i of the part is paired with i + rot_dim/2 (or, `interleaved`, element 2i with 2i + 1); angle =
+// position * inv_freq[i], cos and sin in 32-bit.  The down-projection may lie in rows of its own (`kv_row`).  A layer that reads another layer's cache passes no cache and only gets its queries made.
 //
 // jv_gate_heads: out[t, h*dv + d] = o[h, t, d] * sigmoid(g[t, h*dv + d])  (o as the batched product left it).
 #include "common.cuh"
@@ -18,6 +18,8 @@
 namespace {
 struct PrepareParams {
   const void* row; int row_stride;      // product rows
+  const void* kv_row; int kv_row_stride;   // rows that hold the down-projection at kv_off (the product rows themselves if null)
+  int interleaved;                      // pairs of the rotation: (2i, 2i + 1) instead of (i, i + rot_dim / 2)
   int q_off, kv_off;                    // first column of the queries / of the down-projection (-1: none)
   const void* q_latent;                 // [heads, n, latent_dim] or null
   void* q_out; int q_out_stride;        // [n, heads * (latent_dim + rot_dim)]
@@ -44,15 +46,16 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const PrepareParams
   for (int idx = tid; idx < p.heads * half; idx += blockDim.x) {
     const int hh = idx / half, i = idx - hh * half;
     const T* src = row + p.q_off + (size_t)hh * dh + p.plain_dim;
-    float u = to_f32(src[i]), v = to_f32(src[i + half]);
+    const int i0 = p.interleaved ? 2 * i : i, i1 = p.interleaved ? 2 * i + 1 : i + half;
+    float u = to_f32(src[i0]), v = to_f32(src[i1]);
     if (p.inv_freq != nullptr) {
       float s, c;
       sincosf((float)pos * p.inv_freq[i], &s, &c);
       const float a = u * c - v * s, b = v * c + u * s;
       u = a; v = b;
     }
-    qo[(size_t)hh * dk + p.latent_dim + i] = from_f32<T>(u);
-    qo[(size_t)hh * dk + p.latent_dim + i + half] = from_f32<T>(v);
+    qo[(size_t)hh * dk + p.latent_dim + i0] = from_f32<T>(u);
+    qo[(size_t)hh * dk + p.latent_dim + i1] = from_f32<T>(v);
   }
   if (p.q_latent != nullptr) {
     const T* ql = (const T*)p.q_latent;
@@ -79,7 +82,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const PrepareParams
   const int page = (pos >= 0 && pi < p.table_width) ? p.block_table[(size_t)entry * p.table_width + pi] : -1;
   const bool ok = page >= 0 && page < p.num_pages;
   if (!ok && tid == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
-  const T* kv = row + p.kv_off;
+  const T* kv = (p.kv_row != nullptr ? (const T*)p.kv_row + (size_t)t * p.kv_row_stride : row) + p.kv_off;
   float ss = 0.f;
   for (int i = tid; i < p.latent_dim; i += blockDim.x) { const float v = to_f32(kv[i]); ss += v * v; }
   ss = block_sum(ss, scratch);
@@ -89,15 +92,16 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const PrepareParams
   const TW* w = (const TW*)p.norm_w;
   for (int i = tid; i < p.latent_dim; i += blockDim.x) dst[i] = from_f32<T>(to_f32(kv[i]) * inv * to_f32(w[i]));
   for (int i = tid; i < half; i += blockDim.x) {
-    float u = to_f32(kv[p.latent_dim + i]), v = to_f32(kv[p.latent_dim + i + half]);
+    const int i0 = p.interleaved ? 2 * i : i, i1 = p.interleaved ? 2 * i + 1 : i + half;
+    float u = to_f32(kv[p.latent_dim + i0]), v = to_f32(kv[p.latent_dim + i1]);
     if (p.inv_freq != nullptr) {
       float s, c;
       sincosf((float)pos * p.inv_freq[i], &s, &c);
       const float a = u * c - v * s, b = v * c + u * s;
       u = a; v = b;
     }
-    dst[p.latent_dim + i] = from_f32<T>(u);
-    dst[p.latent_dim + i + half] = from_f32<T>(v);
+    dst[p.latent_dim + i0] = from_f32<T>(u);
+    dst[p.latent_dim + i1] = from_f32<T>(v);
   }
 }
 
@@ -152,11 +156,13 @@ JV_EXPORT int jv_latent_prepare(const void* row, int dtype, int row_stride, int 
                                 void* q_out, int q_out_stride, const int* positions, const int* token_entry,
                                 const int* block_table, int table_width, const float* inv_freq, const void* norm_w,
                                 int norm_dtype, float eps, void* cache, int n, int heads, int plain_dim, int rot_dim,
-                                int latent_dim, int page_size, int num_pages, int* status, cudaStream_t stream) {
+                                int latent_dim, int page_size, int num_pages, const void* kv_row, int kv_row_stride,
+                                int interleaved, int* status, cudaStream_t stream) {
   if (n == 0) return JV_OK;
   if (rot_dim % 2 || heads < 1 || latent_dim < 1) return JV_ERR_UNSUPPORTED;
   PrepareParams p;
   p.row = row; p.row_stride = row_stride; p.q_off = q_off; p.kv_off = kv_off; p.q_latent = q_latent;
+  p.kv_row = kv_row; p.kv_row_stride = kv_row_stride; p.interleaved = interleaved ? 1 : 0;
   p.q_out = q_out; p.q_out_stride = q_out_stride; p.positions = positions; p.token_entry = token_entry;
   p.block_table = block_table; p.table_width = table_width; p.inv_freq = inv_freq; p.norm_w = norm_w; p.eps = eps;
   p.cache = kv_off >= 0 ? cache : nullptr; p.n = n; p.heads = heads; p.plain_dim = plain_dim; p.rot_dim = rot_dim;

@@ -381,6 +381,15 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, token_entry: torch.Tenso
 
 
 # ------------------------------------------------------------------------ attention
+def mask_code(window: int | None = None, chunk: int | None = None) -> int:
+    """The mask of an attention layer as the one number the kernels take (csrc/common.cuh, `first_visible`): n > 0, a
+    query sees its own position and the n - 1 before it; n < 0, it sees the earlier positions of its own chunk of -n
+    positions, chunks counted from position 0; 0, every earlier position."""
+    if window and chunk:
+        raise KernelError("a layer has a window or chunks, not both")
+    return int(window) if window else -int(chunk) if chunk else 0
+
+
 def attn_simt_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
     g = n_q_heads // n_kv_heads
     return 16 // min(g, 16)
@@ -482,9 +491,10 @@ def attn_general_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache:
                      n_work: int, n_q_heads: int, n_kv_heads: int, scale: float, split_size: int = 0, n_splits: int = 0,
                      score_cap: float = 0.0, sigmoid: bool = False, bias: torch.Tensor | None = None,
                      head_scale: torch.Tensor | None = None, dist_bias: torch.Tensor | None = None,
-                     sink: torch.Tensor | None = None) -> None:
+                     sink: torch.Tensor | None = None, window: int = 0) -> None:
     """Paged causal attention on the tensor cores with the options of `attn_simt`: the key size is the key
-    cache's row, the value size and the value heads the value cache's; bfloat16 in, bfloat16 or float32 out."""
+    cache's row, the value size and the value heads the value cache's; bfloat16 in, bfloat16 or float32 out.
+    `window`: the mask as one number (`mask_code`)."""
     n_dist = _score_extras("attn_general_mma", n_q_heads, head_scale, dist_bias, sink)
     for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
@@ -515,7 +525,7 @@ def attn_general_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache:
     _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(part_o),
              _ptr(part_ml), _ptr(counters), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
              block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads,
-             n_kv_heads, n_v_heads, key_dim, value_dim, k_cache.shape[1], k_cache.shape[0], 0, float(scale),
+             n_kv_heads, n_v_heads, key_dim, value_dim, k_cache.shape[1], k_cache.shape[0], int(window), float(scale),
              float(score_cap), 1 if sigmoid else 0, _ptr(bias), _ptr(head_scale), _ptr(dist_bias), n_dist, _ptr(sink),
              int(split_size), int(n_splits), _status_ptr(q.device), _stream()), "attn_general_mma")
 
@@ -644,10 +654,16 @@ def attn_latent_mma_tokens_per_tile(n_heads: int) -> int:
 
 def attn_latent_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                     cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor, n_work: int, n_heads: int,
-                    dk: int, dv: int, scale: float, split_size: int = 0, n_splits: int = 0) -> None:
+                    dk: int, dv: int, scale: float, split_size: int = 0, n_splits: int = 0, window: int = 0,
+                    sink: torch.Tensor | None = None) -> None:
     """Paged causal attention with one key/value head whose key is the cache row [dk] and whose value is the row's
     first dv elements, on the tensor cores (csrc/attn_latent_mma.cu); `work` and the split arguments as for
-    `attn_simt`, with `attn_latent_mma_tokens_per_tile` tokens per prompt tile; out has dv elements per head."""
+    `attn_simt`, with `attn_latent_mma_tokens_per_tile` tokens per prompt tile; out has dv elements per head.
+    `window`: the mask as one number (`mask_code`); `sink` [n_heads] float32: exp(sink) counts once in the denominator."""
+    if sink is not None:
+        _cuda(sink, "sink", torch.float32)
+        if sink.numel() != n_heads:
+            raise KernelError("attn_latent_mma: a sink per head")
     for t, nm in ((q, "q"), (out, "out"), (cache, "cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
@@ -662,11 +678,11 @@ def attn_latent_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache: to
         part_ml = torch.empty(n_work * n_heads * n_splits * 2, dtype=torch.float32, device=q.device)
     f = _fn("attn_latent_mma", "jv_attn_latent_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                      c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+                                                      c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _ptr(part_o), _ptr(part_ml), cache.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
-             n_work, n_heads, dk, dv, cache.shape[1], cache.shape[0], float(scale), int(split_size), int(n_splits),
-             _status_ptr(q.device), _stream()), "attn_latent_mma", launches=2 if n_splits > 0 else 1)
+             n_work, n_heads, dk, dv, cache.shape[1], cache.shape[0], float(scale), int(window), _ptr(sink),
+             int(split_size), int(n_splits), _status_ptr(q.device), _stream()), "attn_latent_mma", launches=2 if n_splits > 0 else 1)
 
 
 _counters: dict[int, torch.Tensor] = {}
@@ -1092,12 +1108,19 @@ def cast_rows(h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 def latent_prepare(row: torch.Tensor, q_off: int, kv_off: int, q_latent: torch.Tensor | None, q_out: torch.Tensor,
                    positions: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor,
                    inv_freq: torch.Tensor | None, norm_w: torch.Tensor | None, eps: float, cache: torch.Tensor | None,
-                   heads: int, plain_dim: int, rot_dim: int, latent_dim: int) -> None:
+                   heads: int, plain_dim: int, rot_dim: int, latent_dim: int, kv_row: torch.Tensor | None = None,
+                   interleaved: bool = False) -> None:
     """Writes a token's cache row [normed latent | rotated key part] and puts its query row together as
     [q_latent | rotated query part] per head (csrc/latent_prepare.cu).  `row`: the product rows
     [queries | down-projection]; `kv_off` < 0 or `cache` None: queries only.  `q_latent` [heads, n, latent_dim]
-    is copied into `q_out` if given (else it is there already)."""
+    is copied into `q_out` if given (else it is there already).  `kv_row`: the rows that hold the down-projection at
+    `kv_off`, where the queries come from a product of their own.  `interleaved`: the rotation pairs element 2i with
+    2i + 1 instead of i with i + rot_dim / 2."""
     _cuda(row, "row", contiguous=False); _cuda(q_out, "q_out", row.dtype)
+    if kv_row is not None:
+        _cuda(kv_row, "kv_row", row.dtype, contiguous=False)
+        if kv_row.shape[0] != row.shape[0] or kv_row.stride(1) != 1:
+            raise KernelError("kv_row has a row per token")
     _cuda(positions, "positions", torch.int32); _cuda(token_entry, "token_entry", torch.int32)
     _cuda(block_table, "block_table", torch.int32)
     n = row.shape[0]
@@ -1118,18 +1141,19 @@ def latent_prepare(row: torch.Tensor, q_off: int, kv_off: int, q_latent: torch.T
         _cuda(cache, "cache", row.dtype); _cuda(norm_w, "latent norm weight")
         if cache.shape[2:] != (1, dk) or norm_w.shape != (latent_dim,):
             raise KernelError(f"cache shape {tuple(cache.shape)} does not fit rows of {dk}")
-        if row.shape[1] < kv_off + dk:
+        if (row if kv_row is None else kv_row).shape[1] < kv_off + dk:
             raise KernelError("the product row is too short for the down-projection")
         num_pages, page_size = cache.shape[0], cache.shape[1]
     f = _fn("latent_prepare", "jv_latent_prepare",
             [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-             c_void_p])
+             c_int, c_int, c_void_p, c_void_p])
     _check(f(row.data_ptr(), _code(row, "row"), row.stride(0), q_off, kv_off if writes else -1, _ptr(q_latent),
              q_out.data_ptr(), q_out.stride(0), positions.data_ptr(), token_entry.data_ptr(), block_table.data_ptr(),
              block_table.shape[1], _ptr(inv_freq), _ptr(norm_w) if writes else 0,
              _code(norm_w, "norm") if writes else 0, float(eps), _ptr(cache) if writes else 0, n, heads, plain_dim,
-             rot_dim, latent_dim, page_size, num_pages, _status_ptr(row.device), _stream()), "latent_prepare")
+             rot_dim, latent_dim, page_size, num_pages, _ptr(kv_row), 0 if kv_row is None else kv_row.stride(0),
+             1 if interleaved else 0, _status_ptr(row.device), _stream()), "latent_prepare")
 
 
 def gate_heads(o: torch.Tensor, gate: torch.Tensor | None) -> torch.Tensor:
@@ -1338,6 +1362,14 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     _cuda(x, "x", torch.float32)
     f = _fn("activation", "jv_softcap", [c_void_p, c_longlong, c_float, c_void_p])
     _check(f(x.data_ptr(), x.numel(), float(cap), _stream()), "softcap")
+    return x
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x <- x * factor, in place on float32 values."""
+    _cuda(x, "x", torch.float32)
+    f = _fn("activation", "jv_scale", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(x.data_ptr(), x.numel(), float(factor), _stream()), "scale")
     return x
 
 
@@ -1568,6 +1600,177 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | N
                                                c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check(f(o.data_ptr(), weight.data_ptr(), _code(weight, "weight"), _ptr(gate), g_stride, out.data_ptr(),
              _code(out, "out"), out.stride(0), n, heads, value_dim, float(eps), _ptr(gates), _stream()), "head_norm_gate")
+    return out
+
+
+# ------------------------------------------------ short convolutions with state (csrc/short_conv.cu)
+SHORT_CONV_MAX_TAPS = 8
+SHORT_CONV_ACTS = {None: 0, "silu": 1}
+
+
+def short_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, cu_seqlens: torch.Tensor,
+               slots: torch.Tensor, n_entries: int, out_dtype: torch.dtype, bias: torch.Tensor | None = None,
+               act: str | None = None, residual: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """A causal convolution over time on each channel of `x` [n, channels] (rows possibly a column range of a wider
+    tensor), `weight` [channels, taps] with the last column on the current token; out = act(conv + bias), or with
+    `residual` x + conv.  `state` [slots, (taps - 1) * channels] float32 (a view of the state rows) holds the last
+    taps - 1 inputs of every sequence and is renewed; a zero row is a sequence's start.  32-bit arithmetic."""
+    _cuda(x, "x", contiguous=False); _cuda(weight, "weight")
+    _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(slots, "slots", torch.int32)
+    n, channels = x.shape
+    taps = weight.shape[1]
+    if x.stride(1) != 1 or weight.shape[0] != channels or not 1 <= taps <= SHORT_CONV_MAX_TAPS or act not in SHORT_CONV_ACTS:
+        raise KernelError("short_conv: shapes do not fit")
+    if bias is not None:
+        _cuda(bias, "bias", weight.dtype)
+        if bias.numel() != channels or residual:
+            raise KernelError("short_conv: a bias per channel, and none where the convolution is added to its input")
+    n_slots = stride = 0
+    if taps > 1:
+        _cuda(state, "state", torch.float32, contiguous=False)
+        if state.stride(1) != 1 or state.shape[1] != (taps - 1) * channels:
+            raise KernelError("short_conv: the state holds taps - 1 inputs of every channel")
+        n_slots, stride = state.shape[0], state.stride(0)
+    if out is None:
+        out = torch.empty((n, channels), dtype=out_dtype, device=x.device)
+    _cuda(out, "out", out_dtype, contiguous=False)
+    if out.shape != x.shape or out.stride(1) != 1:
+        raise KernelError("short_conv: out has the shape of x")
+    f = _fn("short_conv", "jv_short_conv", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p,
+                                            c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                            c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(x.data_ptr(), _code(x, "x"), x.stride(0), out.data_ptr(), _code(out, "out"), out.stride(0),
+             weight.data_ptr(), _ptr(bias), _code(weight, "weight"), _ptr(state) if taps > 1 else 0, stride,
+             cu_seqlens.data_ptr(), slots.data_ptr(), n_entries, n_slots, n, channels, taps, SHORT_CONV_ACTS[act],
+             1 if residual else 0, _status_ptr(x.device), _stream()), "short_conv")
+    return out
+
+
+# ------------------------------------------------ heads prepared one by one (csrc/head_prepare.cu)
+def head_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, positions: torch.Tensor,
+                 token_entry: torch.Tensor, block_table: torch.Tensor, freq: torch.Tensor | None, interleaved: bool,
+                 q_norm_w, k_norm_w, eps: float, value_norm: bool, value_freq: torch.Tensor | None, k_cache, v_cache,
+                 n_q_heads: int, n_k_heads: int, n_v_heads: int, key_dim: int, value_dim: int) -> None:
+    """Per head: RMSNorm of queries and keys with one weight vector [key_dim] shared by the heads (or none), rotation of
+    the first 2 * len(freq) elements (pairs in halves or `interleaved`); values divided by their root mean square
+    (`value_norm`) and rotated by their own position over 2 * len(value_freq) elements; keys and values written to
+    their pages (both caches None: queries only).  32-bit arithmetic."""
+    _cuda(proj, "proj", contiguous=False); _cuda(q_out, "q_out", proj.dtype)
+    _cuda(positions, "positions", torch.int32); _cuda(token_entry, "token_entry", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    n = proj.shape[0]
+    if proj.stride(1) != 1 or q_out.shape != (n, n_q_heads * key_dim):
+        raise KernelError("head_prepare: shapes do not fit")
+    rot = v_rot = 0
+    if freq is not None:
+        _cuda(freq, "freq", torch.float32)
+        rot = 2 * freq.numel()
+    if value_freq is not None:
+        _cuda(value_freq, "value_freq", torch.float32)
+        v_rot = 2 * value_freq.numel()
+    w_code = 0
+    for w in (q_norm_w, k_norm_w):
+        if w is not None:
+            _cuda(w, "norm weight")
+            if w.numel() != key_dim:
+                raise KernelError("head_prepare: the norm's weight has the head's size")
+            w_code = _code(w, "norm weight")
+    if q_norm_w is not None and k_norm_w is not None and q_norm_w.dtype != k_norm_w.dtype:
+        raise KernelError("head_prepare: both norm weights have one type")
+    writes = k_cache is not None
+    page_size = num_pages = 1
+    if writes:
+        _cuda(k_cache, "k_cache", proj.dtype); _cuda(v_cache, "v_cache", proj.dtype)
+        if k_cache.shape[2:] != (n_k_heads, key_dim) or v_cache.shape[2:] != (n_v_heads, value_dim) or \
+                k_cache.shape[:2] != v_cache.shape[:2]:
+            raise KernelError("head_prepare: the caches do not fit the heads")
+        num_pages, page_size = k_cache.shape[0], k_cache.shape[1]
+        if max(k_off + n_k_heads * key_dim, v_off + n_v_heads * value_dim) > proj.shape[1]:
+            raise KernelError("head_prepare: the projection row is too short")
+    if q_off + n_q_heads * key_dim > proj.shape[1]:
+        raise KernelError("head_prepare: the projection row is too short")
+    f = _fn("head_prepare", "jv_head_prepare",
+            [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(proj.data_ptr(), _code(proj, "proj"), proj.stride(0), q_off, k_off, v_off, q_out.data_ptr(),
+             positions.data_ptr(), token_entry.data_ptr(), block_table.data_ptr(), block_table.shape[1], _ptr(freq), rot,
+             _ptr(value_freq), v_rot, 1 if interleaved else 0, _ptr(q_norm_w), _ptr(k_norm_w), w_code, float(eps),
+             1 if value_norm else 0, _ptr(k_cache) if writes else 0, _ptr(v_cache) if writes else 0, n, n_q_heads,
+             n_k_heads, n_v_heads, key_dim, value_dim, page_size, num_pages, _status_ptr(proj.device), _stream()),
+           "head_prepare")
+
+
+def head_rotate(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, interleaved: bool, heads: int, dim: int,
+                sign: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Every head of `x` [n, heads * dim] turned by sign * position * freq[j] over its first 2 * len(freq) elements, in
+    place or into `out` (rows possibly a column range; any of the two types)."""
+    _cuda(x, "x", contiguous=False); _cuda(positions, "positions", torch.int32); _cuda(freq, "freq", torch.float32)
+    out = x if out is None else _cuda(out, "out", contiguous=False)
+    if x.shape[1] != heads * dim or out.shape != x.shape or x.stride(1) != 1 or out.stride(1) != 1 or 2 * freq.numel() > dim:
+        raise KernelError("head_rotate: shapes do not fit")
+    f = _fn("head_prepare", "jv_head_rotate", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p,
+                                               c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+    _check(f(x.data_ptr(), _code(x, "x"), x.stride(0), out.data_ptr(), _code(out, "out"), out.stride(0),
+             positions.data_ptr(), freq.data_ptr(), 2 * freq.numel(), 1 if interleaved else 0, float(sign), x.shape[0],
+             heads, dim, _stream()), "head_rotate")
+    return out
+
+
+def rms_rows(x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.Tensor:
+    """Rows of `x` [n, width] (possibly a column range of a wider tensor) divided by their root mean square, times
+    `weight`; 32-bit arithmetic, the result in x's type."""
+    _cuda(x, "x", contiguous=False)
+    if x.stride(1) != 1:
+        raise KernelError("rms_rows: rows have unit column stride")
+    if weight is not None:
+        _cuda(weight, "weight")
+        if weight.numel() != x.shape[1]:
+            raise KernelError("rms_rows: the weight has the rows' width")
+    out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    f = _fn("head_prepare", "jv_rms_rows", [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_int, c_float,
+                                            c_int, c_int, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), _code(x, "x"), _ptr(weight),
+             0 if weight is None else _code(weight, "weight"), float(eps), x.shape[0], x.shape[1], _stream()), "rms_rows")
+    return out
+
+
+# ------------------------------------------------ state-space mixer: around the state scan (csrc/mamba2.cu)
+def mamba_prepare(xbc: torch.Tensor, b_off: int, c_off: int, dt_raw: torch.Tensor, dt_bias: torch.Tensor,
+                  a_log: torch.Tensor, heads: int, groups: int, state: int) -> torch.Tensor:
+    """Per token and head (C_g, softplus(dt + dt_bias) * B_g, exp(-exp(A_log) * dt)) as float32 [n, heads, 3, state]:
+    query, key and decay of `state_scan`.  B and C are [groups, state] column ranges of the rows `xbc`."""
+    _cuda(xbc, "xbc", contiguous=False); _cuda(dt_raw, "dt", xbc.dtype, contiguous=False)
+    _cuda(dt_bias, "dt_bias"); _cuda(a_log, "A_log", dt_bias.dtype)
+    n = xbc.shape[0]
+    if xbc.stride(1) != 1 or dt_raw.stride(1) != 1 or dt_raw.shape != (n, heads) or heads % groups or \
+            max(b_off, c_off) + groups * state > xbc.shape[1] or dt_bias.numel() != heads or a_log.numel() != heads:
+        raise KernelError("mamba_prepare: shapes do not fit")
+    packed = torch.empty((n, heads, 3, state), dtype=torch.float32, device=xbc.device)
+    f = _fn("mamba2", "jv_mamba_prepare", [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p,
+                                           c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(xbc.data_ptr(), _code(xbc, "xbc"), xbc.stride(0), b_off, c_off, dt_raw.data_ptr(), dt_raw.stride(0),
+             dt_bias.data_ptr(), a_log.data_ptr(), _code(dt_bias, "dt_bias"), packed.data_ptr(), n, heads, groups, state,
+             _stream()), "mamba_prepare")
+    return packed
+
+
+def mamba_finish(o: torch.Tensor, x: torch.Tensor, z: torch.Tensor, skip: torch.Tensor, weight: torch.Tensor,
+                 out: torch.Tensor, heads: int, value_dim: int, norm_groups: int, eps: float) -> torch.Tensor:
+    """y = (o + skip_h * x) * silu(z), divided by the root mean square of each of its `norm_groups` equal parts, times
+    `weight`; o float32 [n, heads * value_dim], x and z column ranges of rows in the compute type; written to `out`."""
+    _cuda(o, "o", torch.float32); _cuda(x, "x", contiguous=False); _cuda(z, "z", x.dtype, contiguous=False)
+    _cuda(skip, "skip"); _cuda(weight, "weight", skip.dtype); _cuda(out, "out", x.dtype, contiguous=False)
+    n, inner = o.shape
+    if inner != heads * value_dim or inner % norm_groups or x.shape != o.shape or z.shape != o.shape or \
+            out.shape != o.shape or x.stride(1) != 1 or z.stride(1) != 1 or out.stride(1) != 1 or skip.numel() != heads or \
+            weight.numel() != inner:
+        raise KernelError("mamba_finish: shapes do not fit")
+    f = _fn("mamba2", "jv_mamba_finish", [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                                          c_int, c_void_p, c_longlong, c_float, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(o.data_ptr(), x.data_ptr(), x.stride(0), z.data_ptr(), z.stride(0), _code(x, "x"), skip.data_ptr(),
+             weight.data_ptr(), _code(skip, "skip"), out.data_ptr(), out.stride(0), float(eps), n, heads, value_dim,
+             norm_groups, _stream()), "mamba_finish")
     return out
 
 

@@ -1,5 +1,5 @@
 from . import (attention, block, dense_mlp, feed_forward, general_attention, latent_attention, mixer_pair, norm,  # noqa: F401
-               position, recurrent, routed_experts, token_input)  # noqa: F401  (register the built-in kinds)
+               position, recurrent, routed_experts, state_space, token_input)  # noqa: F401  (register the built-in kinds)
 from .base import (BuildContext, FixedStateNeed, PagedKVNeed, PagedLayerCache, Part, StateLayerCache, StepContext,
                    TensorSpec)
 from .model import Model

@@ -50,6 +50,7 @@ class PagedKVNeed:
     shared_kv: bool = False       # the values are a leading part of the key rows: one tensor holds both
     v_heads: Optional[int] = None     # value heads and value size where they differ from the keys' (key head g
     v_head_dim: Optional[int] = None  # reads value head g % v_heads)
+    chunk: Optional[int] = None       # keys are read only by the queries of their own chunk of this many positions
 
 
 @dataclass(frozen=True)

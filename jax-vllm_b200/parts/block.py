@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from ..ops import trace_range
-from .base import Part, TensorSpec
+from .base import FixedStateNeed, Part, TensorSpec
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TOKEN_INPUTS, build, register_block
 
 
@@ -25,7 +25,12 @@ class PreNormBlock(Part):
     With `residual_gates` each sublayer's result enters the stream through a gate, element by element:
     h = h + sigmoid(W_g x + b_g) * sublayer(x), x being the sublayer's input.  The gate's product reads the same x
     as the sublayer, so where the sublayer offers its input product (`in_weight`) the gate's matrix is stacked under
-    it and one product serves both; the sum itself is made by the norm that follows (`ops.GatedDelta`)."""
+    it and one product serves both; the sum itself is made by the norm that follows (`ops.GatedDelta`).
+
+    With `input_conv` = (taps, names) what each sublayer reads is u + conv(u), a short causal convolution over time on
+    each channel of the normed stream (csrc/short_conv.cu; the norm hands u on in 32-bit and the sum is rounded to
+    the compute type once).  The last taps - 1 rows of u are state of the sequence, for each sublayer: the block's
+    cache need is then the mixer's followed by one `FixedStateNeed` a sublayer, and it gets a tuple of views."""
 
     def __init__(self, spec, prefix, ctx):
         p = spec.prefix
@@ -40,13 +45,23 @@ class PreNormBlock(Part):
             if not hasattr(self.mixer, "writes_cache"):
                 raise ValueError(f"{p}: this mixer cannot read another layer's cache")
             self.mixer.writes_cache = False
+        self.conv_taps, self.conv_names, self.conv_w = 0, (), [None, None]
+        if spec.input_conv is not None:
+            taps, names = spec.input_conv
+            self.conv_taps = int(taps)
+            if not 1 <= self.conv_taps <= ops.SHORT_CONV_MAX_TAPS:
+                raise ValueError(f"{p}: an input convolution of {taps} taps is not built (1 .. {ops.SHORT_CONV_MAX_TAPS})")
+            self.conv_names = tuple(f"{p}.{n}" for n in names)[:2 if spec.feed_forward is not None else 1]
+            self.kernels = self.kernels + ("short_conv",)
+        need = self.mixer.cache_need()
+        self.mixer_views = len(need) if isinstance(need, (tuple, list)) else None     # None: one view, not a tuple
         gates = spec.residual_gates
         self.gate_names = None if gates is None else tuple(f"{p}.{g}" for g in gates)
         self.gate_w = [None, None]        # per sublayer: the gate's matrix alone, or None where it is stacked
         self.gate_b = [None, None]
         self.packed = [None, None]        # per sublayer: its input matrix with the gate's stacked under it
         if gates is not None:
-            self.kernels = ("dyt", "gemm_simt")
+            self.kernels = self.kernels + ("dyt", "gemm_simt")
 
     def parts(self):
         return tuple(part for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if part is not None)
@@ -60,11 +75,42 @@ class PreNormBlock(Part):
             for name in self.gate_names[:2 if self.feed_forward is not None else 1]:
                 out[name] = TensorSpec((W, W))
                 out[f"{name}.b"] = TensorSpec((W,), kind="vector", init="normal")
+        for name in self.conv_names:
+            out[name] = TensorSpec((self.spec.mixer_norm.size, self.conv_taps), kind="vector", init="normal")
         return out
+
+    def cache_need(self):
+        """What a place of the run order keeps for this layer: the mixer's need, and with an input convolution a
+        state row of (taps - 1) x width 32-bit numbers for each sublayer behind it."""
+        need = self.mixer.cache_need()
+        if not self.conv_names or self.conv_taps < 2:
+            return need
+        own = tuple(FixedStateNeed(((self.conv_taps - 1) * self.spec.mixer_norm.size,), torch.float32) for _ in self.conv_names)
+        return (tuple(need) if self.mixer_views is not None else (need,)) + own
+
+    def _split_cache(self, cache):
+        """(the mixer's cache view(s), the state views of the input convolutions)."""
+        if not self.conv_names or self.conv_taps < 2:
+            return cache, (None, None)
+        k = self.mixer_views if self.mixer_views is not None else 1
+        mixer = tuple(cache[:k]) if self.mixer_views is not None else cache[0]
+        own = tuple(cache[k:]) + (None,)
+        return mixer, own
+
+    def _read(self, norm, i, h, delta, step, conv_state):
+        """What sublayer i reads: the normed stream, with the input convolution added where the layer has one."""
+        if not self.conv_names:
+            return norm.norm(h, delta)
+        u = norm.norm(h, delta, out_dtype=torch.float32)
+        state = conv_state.state if conv_state is not None else None
+        return ops.short_conv(u, self.conv_w[i], state, step.cu_seqlens, step.state_slots, step.n_entries, self.ctx.dtype,
+                              residual=True)
 
     def bind(self, tensors):
         for part in self.parts():
             part.bind(tensors)
+        for i, name in enumerate(self.conv_names):
+            self.conv_w[i] = tensors[name].contiguous()
         if self.gate_names is None:
             return
         subs = (self.mixer, self.feed_forward)
@@ -102,8 +148,9 @@ class PreNormBlock(Part):
 
     def forward(self, h, delta, step, cache):
         step.stream_copy = None
+        cache, conv_state = self._split_cache(cache)
         with trace_range("mixer_norm"):
-            x = self.mixer_norm.norm(h, delta)
+            x = self._read(self.mixer_norm, 0, h, delta, step, conv_state[0])
         with trace_range("mixer"):
             a, z = self._mixer(x, step, cache)
             if z is not None:
@@ -111,7 +158,7 @@ class PreNormBlock(Part):
         if self.feed_forward is None:
             return h, a
         with trace_range("ffn_norm"):
-            x = self.ffn_norm.norm(h, a)
+            x = self._read(self.ffn_norm, 1, h, a, step, conv_state[1])
         with trace_range("feed_forward"):
             y, z = self._feed_forward(x, step)
             return h, (y if z is None else ops.GatedDelta(y, z, self.gate_b[1]))

@@ -3,8 +3,11 @@
     row  = x @ [W_q; W_k; W_v; W_g]^T                    one product over the packed matrix
     q, k   whole-projection RMSNorm, query temperature, rotation of a leading part of every head;
            k, v -> cache (v = k as projected where the spec says so)      csrc/attn_prepare.cu, 32-bit
+           or, head by head: RMSNorm with one weight vector shared by the heads, rotation in halves or interleaved
+           pairs, values unit-normed and rotated by their own position      csrc/head_prepare.cu, 32-bit
     a    = sum_j w_ij v_j over the visible keys, w = softmax(cap(q.k * scale)) or sigmoid(q.k * scale + bias_h)
     o    = a, or a1 - lam * a2 for two score maps, unit-normed; times a sigmoid gate        csrc/attn_finish.cu
+           with rotated values every head of a is first turned back by the query's position   csrc/head_prepare.cu
     y    = o @ W_o^T
 
 Keys have `key_dim` elements a head and values `value_dim`; the value cache has its own shape.  With two score
@@ -71,6 +74,23 @@ class GeneralAttention(Part):
         if self.position is not None and self.position.dim > self.d:
             raise ValueError("rotary dim exceeds the key size")
         self.writes_cache = True
+        self.mask = ops.mask_code(spec.window, spec.chunk)
+        # heads prepared one by one (csrc/head_prepare.cu) where the layer asks for what only that kernel does
+        interleaved = self.position is not None and getattr(self.position, "layout", "halves") == "interleaved"
+        self.by_head = (spec.head_norm_eps is not None or spec.value_norm_eps is not None or spec.rotate_values
+                        or interleaved)
+        if self.by_head and (spec.whole_norm_eps is not None or spec.query_temperature is not None
+                             or spec.values_from_keys or spec.twin is not None):
+            raise ValueError("norms per head, normed or rotated values and interleaved pairs are built without a "
+                             "whole-projection norm, a query temperature, values taken from keys and two score maps")
+        self.interleaved = interleaved
+        self.value_freq = None
+        if spec.rotate_values:
+            if self.position is None or self.dv % 2:
+                raise ValueError("rotated values need a position encoding and an even value size")
+            self.value_freq = self.position.frequencies(self.dv).to(ctx.device)
+        if self.by_head:
+            self.kernels = self.kernels + ("head_prepare",)
         # Which attention kernel: once queries and keys are prepared, a mixer with one softmax map, no cap and
         # values shaped like its keys IS the plain grouped-query attention, and goes the way of that mixer (the
         # tcgen05 kernels for heads of 128, mma.sync for 16/32/64, in bfloat16).  Every other bfloat16 mixer with
@@ -84,8 +104,8 @@ class GeneralAttention(Part):
                  and self.dv == self.d and not self.extras)
         self.plain = self.general = None
         if plain and ops.attn_mma_supports(ctx.dtype, self.d):
-            self.plain = Attention(AttentionSpec(spec.hidden_size, self.hq, self.hk, self.d, spec.scale, prefix=""),
-                                   self.prefix, ctx)
+            self.plain = Attention(AttentionSpec(spec.hidden_size, self.hq, self.hk, self.d, spec.scale, prefix="",
+                                                 window=self.mask or None), self.prefix, ctx)
             self.kernels += tuple(k for k in self.plain.kernels if k not in self.kernels and k != "rope_kv")
         elif ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
             self.general = ops.attn_general_mma_library(self.d, self.dv)
@@ -93,7 +113,7 @@ class GeneralAttention(Part):
         # heads of 128 with sigmoid weights, or with a softmax that has a temperature per head, a bias by distance or a
         # sink: prompt portions that fill a 128-row tile go to the tcgen05 kernel
         self.big_tiles = (self.general is not None and not spec.score_cap and self.hv == self.hk and self.dv == self.d == 128
-                          and spec.twin is None and (spec.weights == "sigmoid") != bool(self.extras))
+                          and spec.twin is None and (spec.weights == "sigmoid") != bool(self.extras) and not self.mask)
         if self.big_tiles:
             self.kernels += ("attn_tcgen05",)
         self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
@@ -124,6 +144,9 @@ class GeneralAttention(Part):
         if s.whole_norm_eps is not None:
             specs[n["q_norm"]] = TensorSpec((self.hq * self.d,), kind="vector", init="ones_normal")
             specs[n["k_norm"]] = TensorSpec((self.hk * self.d,), kind="vector", init="ones_normal")
+        if s.head_norm_eps is not None:
+            specs[n["q_norm"]] = TensorSpec((self.d,), kind="vector", init="ones_normal")
+            specs[n["k_norm"]] = TensorSpec((self.d,), kind="vector", init="ones_normal")
         if s.score_bias:
             specs[n["bias"]] = TensorSpec((self.h,), kind="vector", init="normal")
         if s.twin is not None:
@@ -156,7 +179,7 @@ class GeneralAttention(Part):
             mats = [m.to(torch.float32) for m in mats]
         self.w_in = torch.cat(mats, dim=0).contiguous()
         self.w_o = self.compute_weight(tensors[n["o"]], self.ctx).contiguous()
-        if s.whole_norm_eps is not None:
+        if s.whole_norm_eps is not None or s.head_norm_eps is not None:
             self.q_norm, self.k_norm = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
             if self.q_norm.dtype != self.k_norm.dtype:
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
@@ -177,9 +200,10 @@ class GeneralAttention(Part):
 
     # ---------------------------------------------------------------------- cache
     def cache_need(self):
+        s = self.spec
         if self.hv == self.hk and self.dv == self.d:
-            return PagedKVNeed(self.hk, self.d, None)
-        return PagedKVNeed(self.hk, self.d, None, v_heads=self.hv, v_head_dim=self.dv)
+            return PagedKVNeed(self.hk, self.d, s.window or None, chunk=s.chunk or None)
+        return PagedKVNeed(self.hk, self.d, s.window or None, v_heads=self.hv, v_head_dim=self.dv, chunk=s.chunk or None)
 
     def tile_classes(self, page_size: int):
         if self.plain is not None:
@@ -221,12 +245,25 @@ class GeneralAttention(Part):
         writes = self.writes_cache and cache.writes
         q = torch.empty((n, self.hq * self.d), dtype=dt, device=row.device)
         coef, every = s.query_temperature if s.query_temperature is not None else (0.0, 0)
-        ops.attn_prepare(row, 0, self.k_off, self.v_off, q, step.positions, step.token_entry, table,
-                         self.position.table() if self.position is not None else None, self.q_norm, self.k_norm,
-                         s.whole_norm_eps or 0.0, coef, every, cache.k if writes else None, cache.v if writes else None,
-                         self.hq, self.hk, self.hv, self.d, self.dv)
+        freq = self.position.table() if self.position is not None else None
+        if self.by_head:
+            ops.head_prepare(row, 0, self.k_off, self.v_off, q, step.positions, step.token_entry, table, freq,
+                             self.interleaved, self.q_norm, self.k_norm, s.head_norm_eps or s.value_norm_eps or 0.0,
+                             s.value_norm_eps is not None, self.value_freq, cache.k if writes else None,
+                             cache.v if writes else None, self.hq, self.hk, self.hv, self.d, self.dv)
+        else:
+            ops.attn_prepare(row, 0, self.k_off, self.v_off, q, step.positions, step.token_entry, table, freq,
+                             self.q_norm, self.k_norm, s.whole_norm_eps or 0.0, coef, every, cache.k if writes else None,
+                             cache.v if writes else None, self.hq, self.hk, self.hv, self.d, self.dv)
         gate = row[:, self.g_off:self.g_off + self.g_rows] if s.gate is not None else None
         twin = s.twin
+        if self.value_freq is not None and twin is None and gate is None:
+            # the heads' outputs are turned back by the query's position, on the way to where they are wanted
+            a = out if out.is_contiguous() else torch.empty((n, self.hq * self.dv), dtype=dt, device=row.device)
+            self.attend(q, a, step, cache, table)
+            return ops.head_rotate(a, step.positions, self.value_freq, self.interleaved, self.h, self.dv, sign=-1.0, out=out)
+        if self.value_freq is not None:
+            raise ValueError("rotated values with a gate or two score maps are not built")
         direct = twin is None and gate is None and out.is_contiguous()
         # two maps are subtracted in 32-bit: the attention kernel leaves them as floats
         a = out if direct else torch.empty((n, self.hq * self.dv), dtype=torch.float32 if twin is not None else dt,
@@ -248,10 +285,11 @@ class GeneralAttention(Part):
             extra.update(head_scale=self.head_scale, dist_bias=self.dist_bias, sink=self.sink)
         if self.general is not None:
             def kernel(work, n_work, **split):
-                ops.attn_general_mma(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, s.scale, **split, **extra)
+                ops.attn_general_mma(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, s.scale,
+                                     window=self.mask, **split, **extra)
         else:
             def kernel(work, n_work, **split):
-                ops.attn_simt(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, 0, s.scale,
+                ops.attn_simt(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, self.mask, s.scale,
                               v_dim=self.dv, **split, **extra)
         for cls in self.tile_classes(cache.k.shape[1]):
             work, n_work = step.tile_work[cls]

@@ -76,7 +76,7 @@ class Model(Part):
         names.update(getattr(self.final_norm, "kernels", ()))
         if self.pass_table is not None or self.spec.pass_vectors is not None:
             names.add("dyt")
-        if self.spec.logit_softcap:
+        if self.spec.logit_softcap or self.spec.logit_scale is not None:
             names.add("activation")
         if self.ctx.dtype == torch.bfloat16:
             names.update(("linear_skinny", "linear_stream"))
@@ -96,8 +96,11 @@ class Model(Part):
     def cache_needs(self):
         """Per place in the run order: what the layer there needs to keep, or None (nothing, or
         it reads another place's cache)."""
-        return [self.layers[i].mixer.cache_need() if self.place_cache[k] == k else None
-                for k, i in enumerate(self.order)]
+        def need(block):          # an arrangement that keeps something of its own says so; else it is the mixer's
+            f = getattr(block, "cache_need", None)
+            return f() if f is not None else block.mixer.cache_need()
+
+        return [need(self.layers[i]) if self.place_cache[k] == k else None for k, i in enumerate(self.order)]
 
     def tile_classes(self, page_size: int):
         """The attention work lists that the mixers of this model want (see BatchBuilder)."""
@@ -143,6 +146,8 @@ class Model(Part):
             x = self.final_norm.gather(h, delta, step.logit_rows)
         with ops.trace_range("lm_head"):
             logits = ops.linear(x, self.lm_head, torch.float32)
+            if self.spec.logit_scale is not None:
+                ops.scale_(logits, self.spec.logit_scale)
             if self.spec.logit_softcap:
                 ops.softcap_(logits, self.spec.logit_softcap)
             return logits

@@ -1,5 +1,7 @@
 """RMSNorm over the hidden axis: y = h * rsqrt(mean(h^2) + eps) * weight, in 32-bit
-(jllm/model/common.py:44-48), fused with the residual sum before it."""
+(jllm/model/common.py:44-48), fused with the residual sum before it.  With an `offset` the
+stored weight is kept around zero and weight + offset multiplies (formed once, in 32-bit,
+when the weights are bound)."""
 
 from __future__ import annotations
 
@@ -13,19 +15,22 @@ class RMSNorm(Part):
 
     def __init__(self, spec, prefix, ctx):
         self.size, self.eps = spec.size, float(spec.eps)
+        self.offset = float(getattr(spec, "offset", 0.0))
         self.name = f"{prefix}.{spec.name}" if prefix else spec.name
         self.ctx = ctx
         self.weight = None
 
     def tensor_specs(self):
-        return {self.name: TensorSpec((self.size,), kind="vector", init="ones_normal")}
+        return {self.name: TensorSpec((self.size,), kind="vector", init="normal" if self.offset else "ones_normal")}
 
     def bind(self, tensors):
-        self.weight = tensors[self.name].contiguous()
+        w = tensors[self.name]
+        self.weight = (w.float() + self.offset).contiguous() if self.offset else w.contiguous()
 
-    def norm(self, h, delta=None):
-        """x = norm(h + delta); h is updated in place with the sum."""
-        return ops.rmsnorm(h, self.weight, self.eps, self.ctx.dtype, delta=delta)
+    def norm(self, h, delta=None, out_dtype=None):
+        """x = norm(h + delta); h is updated in place with the sum.  `out_dtype`: the type of x (the compute type
+        by default; float32 for a reader that goes on in 32-bit)."""
+        return ops.rmsnorm(h, self.weight, self.eps, out_dtype or self.ctx.dtype, delta=delta)
 
     def gather(self, h, delta, rows):
         """x[i] = norm(h[rows[i]] + delta[rows[i]]); h is left as it is."""
@@ -59,8 +64,8 @@ class DynamicTanh(Part):
         self.bias = tensors[f"{self.name}.b"].to(self.weight.dtype).contiguous()
         self.alpha = float(tensors[f"{self.name}.alpha"].float().item())
 
-    def norm(self, h, delta=None):
-        return ops.gated_add_dyt(h, delta, self.alpha, self.weight, self.bias, self.ctx.dtype)
+    def norm(self, h, delta=None, out_dtype=None):
+        return ops.gated_add_dyt(h, delta, self.alpha, self.weight, self.bias, out_dtype or self.ctx.dtype)
 
     def gather(self, h, delta, rows):
         return ops.gated_add_dyt(h, delta, self.alpha, self.weight, self.bias, self.ctx.dtype, rows=rows)

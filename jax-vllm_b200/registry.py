@@ -60,6 +60,9 @@ def _register_builtin() -> None:
     from .models.nufapel import ARCHITECTURE as NUFAPEL, NufapelConfig
 
     register_architecture(NUFAPEL, NufapelConfig)
+    from .models.gogivik import ARCHITECTURE as GOGIVIK, GogivikConfig
+
+    register_architecture(GOGIVIK, GogivikConfig)
 
 
 _register_builtin()
