@@ -692,6 +692,8 @@ def design(name: str, layers, sizes, steps, warmup) -> int:
         return design_loselix(layers or 3, sizes, steps, warmup)
     if name == "nufapel":
         return design_nufapel(layers or 3, sizes, steps, warmup)
+    if name == "gogivik":
+        return design_gogivik(layers or 3, sizes, steps, warmup)
     if name != "guronex":
         print(f"bench.py: no design {name!r}")
         return 2
@@ -916,6 +918,194 @@ def design_nufapel(layers, sizes, steps, warmup) -> int:
     return 0
 
 
+# ------------------------------------------------------------------ the Gogivik design beside Loselix
+# Layer sizes for `--design gogivik`: three layers (chunked attention with rotated values; a state-space layer; latent
+# attention with a window and a sink), each over a dense feed-forward and behind input convolutions of three taps,
+# beside three Loselix softmax-attention layers of equal width, heads and feed-forward.  "w2k": the width of a 1B-class
+# model; "w4k": an 8B-class width.  The latent sizes are those of published latent-attention models (a latent of 512
+# with a rotated part of 64, queries through a latent of 1,536), the state-space sizes those of published Mamba-2
+# models (heads of 64 values, 128 state channels, four taps).
+GOGIVIK_SIZES = {
+    "w2k": dict(width=2048, heads=16, kv=4, dim=128, vdim=128, chunk=8192, ssm=(64, 64, 128, 1), lat=(16, 128, 64, 128, 512, 1536),
+                window=1024, ff=8192),
+    "w4k": dict(width=4096, heads=32, kv=8, dim=128, vdim=128, chunk=8192, ssm=(128, 64, 128, 8), lat=(32, 128, 64, 128, 512, 1536),
+                window=1024, ff=16384),
+    "small": dict(width=1024, heads=16, kv=4, dim=64, vdim=64, chunk=1536, ssm=(32, 64, 64, 2), lat=(8, 64, 32, 64, 256, 512),
+                  window=512, ff=4096),
+}
+GOGIVIK_KINDS = ("attention", "state_space", "latent_attention")
+
+
+def gogivik_configs(z, layers, vocab=32000):
+    H, G = z["heads"], z["kv"]
+    sh, sv, sn, sg = z["ssm"]
+    lh, ld, lr, lv, lc, lq = z["lat"]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    three = [{"type": "attention", "mlp": dense,
+              "mixer": {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                        "mask": {"size": z["chunk"]}, "rot": {"base": 5e5, "dims": z["dim"], "scaling": {"factor": 8.0}}}},
+             {"type": "mamba2", "mlp": dense,
+              "mixer": {"heads": sh, "vdim": sv, "state": sn, "groups": sg, "norm_groups": sg, "conv": 4}},
+             {"type": "latent_attention", "mlp": dense,
+              "mixer": {"heads": lh, "dim": ld, "rot_dim": lr, "vdim": lv, "kv_rank": lc, "q_rank": lq,
+                        "scale": (ld + lr) ** -0.5, "mask": {"size": z["window"]}, "rot": {"base": 5e5, "dims": lr}}}]
+    gogivik = {"architecture": "Gogivik", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+               "logit_scale": 1.0, "layers": [json.loads(json.dumps(three[i % 3])) for i in range(layers)]}
+    soft = {"type": "attention_2", "mlp": {"kind": "dense", "ff": z["ff"]},
+            "mixer": {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                      "rot": {"base": 5e5, "dims": z["dim"] // 2}}}
+    loselix = {"architecture": "Loselix", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+               "layers": [json.loads(json.dumps(soft)) for _ in range(layers)]}
+    return gogivik, loselix
+
+
+def gogivik_parts(model, z, layer_index, batch, tokens, reps, pk, sm_mhz):
+    """Layer `layer_index` of a Gogivik model in parts, each alone: the attention kernel (or, for the state-space layer,
+    the recurrence from the projected row to the normed heads: convolution, step sizes, scan, gated norm, and the scan
+    alone), the preparation of the heads, the input convolution, the whole mixer, the whole feed-forward.  One prompt
+    of `tokens` tokens, then one decode step of `batch` requests at CONTEXT tokens.  Rooflines as for the other
+    designs; a mask counts: the pairs and the cache rows are those that the chunk or the window lets a query see."""
+    import torch
+    from jax_vllm_b200 import make_driver, ops
+    from jax_vllm_b200.engine import StepEntry
+    W = z["width"]
+    flush = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")
+    layer = model.layers[layer_index]
+    mixer, ff = layer.mixer, layer.feed_forward
+    kind = GOGIVIK_KINDS[layer_index % 3]
+    out = {}
+
+    def seen(pos, mask):                      # keys that a query at `pos` sees
+        return pos + 1 if not mask else min(pos + 1, mask) if mask > 0 else pos % (-mask) + 1
+
+    for phase in ("prefill", "decode"):
+        if phase == "prefill":
+            driver = make_driver(model, max_num_seqs=1, max_model_len=tokens + 16, block_size=PAGE, prefix_cache=False,
+                                 max_tokens_per_step=tokens, cuda_graphs=False)
+            rc = driver.cache.admit("p")
+            driver.cache.grow(rc, tokens)
+            entries = [StepEntry(rc, [(i * 7919 + 13) % 1000 for i in range(tokens)], (tokens - 1,))]
+            n, seqs, positions = tokens, 1, list(range(tokens))
+        else:
+            driver = make_driver(model, max_num_seqs=batch, max_model_len=CONTEXT + 64, block_size=PAGE, prefix_cache=False,
+                                 cuda_graphs=False)
+            rcs = fake_context(driver, batch, CONTEXT)
+            for rc in rcs:
+                driver.cache.grow(rc, rc.num_tokens + 1)
+            entries = [StepEntry(rc, [b], (0,)) for b, rc in enumerate(rcs)]
+            n, seqs, positions = batch, batch, [CONTEXT] * batch
+        step = driver.runner.builder.build(entries)
+        views = driver.runner.layer_caches[layer_index]
+        cache, conv_state = layer._split_cache(views)
+        x = (torch.randn((n, W), device="cuda") * 0.5).to(torch.bfloat16)
+        xf = x.float()
+        jobs = []
+        bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        if kind == "state_space":
+            row = (torch.randn((n, mixer.in_rows), device="cuda") * 0.5).to(torch.bfloat16)
+            heads = torch.empty((n, mixer.heads_out), dtype=torch.bfloat16, device="cuda")
+            fma = n * mixer.h * mixer.n * mixer.e * 3                          # decay, write, read
+            nbytes = seqs * 2 * mixer.h * mixer.n * mixer.e * 4 + n * mixer.in_rows * 2 + n * mixer.heads_out * 2
+            roof = (fma / (FP32_LANES * sm_mhz * 1e6) * 1e6, nbytes / bw * 1e6, "fp32 lanes")
+            jobs.append(("recurrence", lambda: mixer.from_projection(row, step, cache, heads), roof))
+            xbc = (torch.randn((n, mixer.conv_channels), device="cuda") * 0.5).to(torch.bfloat16)
+            packed = ops.mamba_prepare(xbc, mixer.inner, mixer.inner + mixer.g * mixer.n, row[:, -mixer.h:], mixer.dt_bias,
+                                       mixer.a_log, mixer.h, mixer.g, mixer.n)
+            jobs.append(("state scan", lambda: ops.state_scan(packed, xbc, 0, cache.state, step.cu_seqlens, step.state_slots,
+                                                              step.n_entries, mixer.e), roof))
+            cb = n * mixer.conv_channels * 4 + n * 0
+            jobs.append(("mixer convolution", lambda: ops.short_conv(row[:, mixer.inner:mixer.inner + mixer.conv_channels],
+                                                                     mixer.conv_w, cache.state[:, mixer.h * mixer.n * mixer.e:],
+                                                                     step.cu_seqlens, step.state_slots, step.n_entries,
+                                                                     torch.bfloat16, bias=mixer.conv_b, act="silu"),
+                         (0.0, cb / bw * 1e6, "flops")))
+        else:
+            table = step.block_tables[cache.group]
+            mask = mixer.mask
+            pairs = sum(seen(p, mask) for p in positions)
+            if phase == "prefill":
+                keys = tokens
+            else:
+                keys = batch * seen(CONTEXT, mask)
+            if kind == "attention":
+                q = torch.randn((n, mixer.hq * mixer.d), device="cuda").to(torch.bfloat16)
+                a = torch.empty((n, mixer.hq * mixer.dv), dtype=torch.bfloat16, device="cuda")
+                attn = lambda: mixer.attend(q, a, step, cache, table)
+                flops = 2 * mixer.hq * (mixer.d + mixer.dv) * pairs
+                nbytes = keys * (mixer.hk * mixer.d + mixer.hv * mixer.dv) * 2 + n * mixer.hq * (mixer.d + mixer.dv) * 2
+                rowp = (torch.randn((n, mixer.in_rows), device="cuda") * 0.5).to(torch.bfloat16)
+                prep = lambda: ops.head_prepare(rowp, 0, mixer.k_off, mixer.v_off, q, step.positions, step.token_entry, table,
+                                                mixer.position.table(), False, mixer.q_norm, mixer.k_norm, 1e-5, True,
+                                                mixer.value_freq, cache.k, cache.v, mixer.hq, mixer.hk, mixer.hv, mixer.d, mixer.dv)
+                pb = n * mixer.in_rows * 2 * 2
+                jobs.append(("head preparation", prep, (0.0, pb / bw * 1e6, "flops")))
+                jobs.append(("output rotation", lambda: ops.head_rotate(a, step.positions, mixer.value_freq, False, mixer.h,
+                                                                        mixer.dv, sign=-1.0),
+                             (0.0, n * mixer.hq * mixer.dv * 4 / bw * 1e6, "flops")))
+            else:
+                q = torch.randn((n, mixer.h * mixer.dk), device="cuda").to(torch.bfloat16)
+                attn = lambda: mixer.attend(q, step, cache, table)
+                flops = 2 * mixer.h * (mixer.dk + mixer.dc) * pairs
+                nbytes = keys * mixer.dk * 2 + n * mixer.h * (mixer.dk + mixer.dc) * 2
+            jobs.append(("attention kernel", attn, (flops / tf * 1e6, nbytes / bw * 1e6, "flops")))
+        if conv_state[0] is not None:
+            jobs.append(("input convolution", lambda: ops.short_conv(xf, layer.conv_w[0], conv_state[0].state, step.cu_seqlens,
+                                                                     step.state_slots, step.n_entries, torch.bfloat16,
+                                                                     residual=True), (0.0, n * W * 6 / bw * 1e6, "flops")))
+        jobs.append(("mixer", lambda: mixer.forward(x, step, cache), None))
+        ff_flops, ff_bytes = 2 * n * 2 * z["ff"] * W, 2 * z["ff"] * W * 2
+        jobs.append(("feed-forward", lambda: ff.forward(x, step), (ff_flops / tf * 1e6, ff_bytes / bw * 1e6, "flops")))
+        res = {}
+        for name, fn, roof in jobs:
+            us = time_part(fn, reps, flush)
+            res[name] = {"us": round(us, 1)}
+            if roof is not None:
+                t_math, t_bytes, unit = roof
+                ideal = max(t_math, t_bytes)
+                res[name].update(roofline_us=round(ideal, 1), bound=unit if t_math >= t_bytes else "bytes",
+                                 of_roofline=round(ideal / us, 3))
+        driver.runner.check_kernels()
+        out[phase] = res
+        del driver
+        torch.cuda.empty_cache()
+    return out
+
+
+def design_gogivik(layers, sizes, steps, warmup) -> int:
+    import torch
+    from jax_vllm_b200 import random_model, registry
+    pk, pk_src = peaks()
+    sizes = [t for t in sizes if t in GOGIVIK_SIZES] or ["w2k", "w4k"]
+    out = {"design": "gogivik", "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_batch": 8, "context": CONTEXT,
+           "dtype": "bf16", "data": "synthetic (random weights, seed 5)", "peaks": pk, "peak_source": pk_src, "sizes": {}}
+    for tag in sizes:
+        z = GOGIVIK_SIZES[tag]
+        g_cfg, l_cfg = gogivik_configs(z, layers)
+        row = {"gogivik": {"config": {k: v for k, v in z.items()}},
+               "loselix": {"config": {"width": z["width"], "heads": z["heads"], "kv": z["kv"], "dim": z["dim"], "ff": z["ff"]}}}
+        for kind, cfg in (("gogivik", g_cfg), ("loselix", l_cfg)):
+            model = random_model(registry.config_from_dict(cfg), seed=5, dtype="bf16", device="cuda:0")
+            with ClockSampler() as clocks:
+                pms = time_prefill(model, PREFILL_TOKENS, warmup=2, reps=5)
+                dms, launches, _, _ = time_decode(model, 8, steps, warmup)
+            row[kind].update(prefill_tok_s=round(PREFILL_TOKENS / (pms / 1e3), 1), prefill_ms=round(pms, 3),
+                             decode_tok_s=round(8 / (dms / 1e3), 1), decode_ms_per_step=round(dms, 4),
+                             decode_launches_per_step=launches, clocks=clocks.summary)
+            if kind == "loselix":
+                lz = dict(z, soft=(z["dim"], z["vdim"], z["dim"] // 2))
+                row[kind]["parts"] = design_parts(model, kind, lz, 0, 8, PREFILL_TOKENS, 7, pk)
+            else:
+                mhz = float(clocks.summary.get("sm_max_mhz") or 1965.0)
+                row[kind]["fp32_peak_tflops"] = round(2 * FP32_LANES * mhz * 1e6 / 1e12, 1)
+                row[kind]["parts"] = {GOGIVIK_KINDS[i]: gogivik_parts(model, z, i, 8, PREFILL_TOKENS, 7, pk, mhz)
+                                      for i in range(min(3, layers))}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][tag] = row
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm():
     why = ("the reference (jllm) needs jax, jaxlib and equinox and the hatchling build backend; none is installed "
            "and none is in the offline wheelhouse, so it can neither be installed nor run here")
@@ -942,12 +1132,12 @@ def main():
     ap.add_argument("--with-workloads", action="store_true",
                     help="after the headline run, also run the two serving workloads and add their lines under `workloads`")
     ap.add_argument("--design", default=None, metavar="NAME",
-                    help="guronex, loselix or nufapel: that design's prefill and decode throughput at a few layer sizes "
+                    help="guronex, loselix, nufapel or gogivik: that design's prefill and decode throughput at a few layer sizes "
                          "beside its closest neighbour of equal size (Qwen3; for nufapel, Loselix), with the rooflines of "
                          "its kernels (see design())")
     ap.add_argument("--sizes", default="lite,mid,row576",
                     help="with --design: which of its layer sizes, comma-separated (guronex: lite,mid,row576; loselix: "
-                         "w2k,w4k,mix, all by default; nufapel: w2k,w4k,small, the first two by default)")
+                         "w2k,w4k,mix, all by default; nufapel and gogivik: w2k,w4k,small, the first two by default)")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()

@@ -48,15 +48,15 @@ __global__ void __launch_bounds__(THREADS) short_conv_kernel(const ConvParams p)
   if (c >= p.channels) return;
   const int t_begin = p.cu_seqlens[entry], q = p.cu_seqlens[entry + 1] - t_begin;
   const int i0 = seg * SEG, i1 = min(q, i0 + SEG);
-  const int slot = p.slots[entry];
-  if (slot < 0 || slot >= p.n_slots) {
+  constexpr int K = TAPS - 1;
+  const int slot = K > 0 ? p.slots[entry] : 0;        // one tap keeps nothing
+  if (K > 0 && (slot < 0 || slot >= p.n_slots)) {
     if (threadIdx.x == 0) atomicOr(p.status, JV_STATUS_BAD_ROW);
     return;
   }
   const TI* in = (const TI*)p.in + c;
   TO* out = (TO*)p.out + c;
-  float* st = p.state + (size_t)slot * p.state_stride + c;
-  constexpr int K = TAPS - 1;
+  float* st = K > 0 ? p.state + (size_t)slot * p.state_stride + c : nullptr;
   float wt[TAPS];
 #pragma unroll
   for (int j = 0; j < TAPS; ++j) wt[j] = to_f32(((const TW*)p.w)[(size_t)c * TAPS + j]);

@@ -221,4 +221,4 @@ def forward(cfg: dict, w: dict, tokens, taps=None) -> torch.Tensor:
             x = x + feed_forward(u, w, f"{p}.mlp")
         if taps is not None:
             taps.append(x.clone())
-    return offset_norm(x, w["final.norm"], eps) @ w["head"].T * float(cfg["logit_scale"])
+    return offset_norm(x, w["final.norm"], eps) @ w["head"].T * float(cfg.get("logit_scale", 1.0))
