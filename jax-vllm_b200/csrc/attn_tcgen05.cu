@@ -56,6 +56,7 @@ struct Params {
   // softmax only: the scaled score of head h is multiplied by head_scale[h]; dist_bias[h][min(pos - j, n_dist - 1)] is
   // added to the score of key j (untouched by the scales); exp(sink[h]) counts once in the denominator.  Each may be null.
   const float* head_scale; const float* dist_bias; int n_dist; const float* sink;
+  int window;                  // the mask as one number (common.cuh, first_visible): 0, a window (> 0) or chunks (< 0)
   int* status;
 };
 
@@ -216,7 +217,8 @@ struct Shared {
 struct Item {
   int entry, kv_head, q_first;      // request of the batch, kv head, first row of the tile among all tokens
   int tokens_here, pos_first;       // tokens in the tile, position of the first
-  int j_hi, n_tiles;                // keys [0, j_hi) are visible to the last row; key tiles
+  int j_lo, j_hi;                   // keys [j_lo, j_hi) are visible to some row: j_lo is the first row's first visible key
+  int tile0, n_tiles;               // the first key tile (keys tile0 * BN ..) and the number of key tiles
 };
 
 __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map,
@@ -255,7 +257,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
     it.tokens_here = min(p.tokens_per_tile, q_len - q_off);
     it.pos_first = p.start_pos[it.entry] + q_off;
     it.j_hi = it.pos_first + it.tokens_here;
-    it.n_tiles = it.tokens_here > 0 ? (it.j_hi + BN - 1) / BN : 0;
+    it.j_lo = first_visible(it.pos_first, p.window);
+    it.tile0 = it.j_lo / BN;
+    it.n_tiles = it.tokens_here > 0 ? (it.j_hi + BN - 1) / BN - it.tile0 : 0;
     return it;
   };
 
@@ -317,10 +321,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       // page ids of a tile: lane i reads the i-th (a tile has at most 16 pages); -1 = no page needed or none there
+      // (a page whose keys all lie before the first visible one is not needed, and may have been given back)
       auto tile_pages = [&](int j) -> int {
-        const int pi = j * pages_per_tile + lane;
+        const int pi = (j + it.tile0) * pages_per_tile + lane;
         int page = -1;
-        if (j < it.n_tiles && lane < pages_per_tile && pi * P < it.j_hi && pi < p.table_width) {
+        if (j < it.n_tiles && lane < pages_per_tile && pi * P < it.j_hi && (pi + 1) * P > it.j_lo && pi < p.table_width) {
           page = p.block_table[(size_t)it.entry * p.table_width + pi];
           if (page < 0 || page >= p.num_pages) { atomicOr(p.status, JV_STATUS_BAD_PAGE); page = -1; }
         }
@@ -454,9 +459,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       const Item it = upcoming;
       ++r_next;
       more = next_item(r_next, upcoming);
-      const int n_tiles = it.n_tiles, j_hi = it.j_hi, pos_first = it.pos_first;
+      const int n_tiles = it.n_tiles, j_hi = it.j_hi, pos_first = it.pos_first, tile0 = it.tile0;
       const bool row_ok = t < it.tokens_here && hh < G;
       const int pos = row_ok ? pos_first + t : -1;
+      const int vis_first = first_visible(pos, p.window);                    // this row's first visible key
+      const int vis_first_last = first_visible(pos_first + it.tokens_here - 1, p.window);   // the last row's
       // sigmoid weights: the bias of this row's head, in the exponent's unit
       const float bias_log2 = (p.sigmoid && p.bias != nullptr && row_ok) ? p.bias[it.kv_head * G + hh] * LOG2E : 0.f;
       // With a head's own scale or a bias by distance the scores are first brought to the exponent's unit, s * scale *
@@ -477,8 +484,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         if (ok) ok = mbar_wait(&sh->s_full[gt & 1], (gt >> 1) & 1);
         ok = __all_sync(0xffffffffu, ok);
         const uint32_t s_addr = tmem + lane_addr + (gt & 1) * 128 + half * 64;
-        const int key0 = j * BN + half * 64;                     // first key of this thread's 64
-        const bool need_mask = j * BN + BN > j_hi || j * BN + BN - 1 > pos_first;   // block-uniform
+        const int jt = j + tile0;                                // the tile among all key tiles of the request
+        const int key0 = jt * BN + half * 64;                    // first key of this thread's 64
+        const bool need_mask = jt * BN + BN > j_hi || jt * BN + BN - 1 > pos_first || jt * BN < vis_first_last;   // block-uniform
         uint32_t sr[2][32];
         float my_max = -INFINITY;
         if (ok) {
@@ -502,11 +510,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           // tile of an item has keys to hide
           if (need_mask) {
             const int last = min(pos, j_hi - 1) - key0;          // the last of this thread's 64 keys that counts
+            const int first = vis_first - key0;                  // and the first (a window, a chunk)
 #pragma unroll
             for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (c * 32 + i > last) sr[c][i] = __float_as_uint(-INFINITY);
+                if (c * 32 + i > last || c * 32 + i < first) sr[c][i] = __float_as_uint(-INFINITY);
           }
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -589,20 +598,25 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
           tmem_st32_bits(tmem + lane_addr + TMEM_P + (gt & 1) * 64 + half * 32, pw);
         }
         l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
-        // ---- in an item's last tile the value rows past the end become zero (they may hold anything)
-        if (j == n_tiles - 1 && j_hi < j * BN + BN) {
+        // ---- in an item's last tile the value rows past the end become zero (they may hold anything), and in its first
+        // tile those before the first visible key (their pages may not have been loaded)
+        const int rows_before = j == 0 ? it.j_lo - jt * BN : 0;
+        const int rows_upto = (j == n_tiles - 1 && j_hi < jt * BN + BN) ? j_hi - jt * BN : BN;
+        if (rows_before > 0 || rows_upto < BN) {
           const int s = gt % V_STAGES;
           ok = __all_sync(0xffffffffu, mbar_wait(&sh->v_full[s], (gt / V_STAGES) & 1));
           if (ok) {
-            for (int i = (threadIdx.x - 64); i < (j * BN + BN - j_hi) * 16; i += SOFTMAX_THREADS) {
-              const int key_row = (j_hi - j * BN) + i / 16, part = i % 16;     // 16 chunks of 16 bytes per row (both halves)
+            const int n_zero = rows_before + (BN - rows_upto);
+            for (int i = (threadIdx.x - 64); i < n_zero * 16; i += SOFTMAX_THREADS) {
+              const int z = i / 16, part = i % 16;                // 16 chunks of 16 bytes per row (both halves)
+              const int key_row = z < rows_before ? z : rows_upto + (z - rows_before);
               *reinterpret_cast<uint4*>(v_s + s * TILE_BYTES + (part >> 3) * HALF_BYTES + key_row * 128 + (part & 7) * 16) =
                   make_uint4(0, 0, 0, 0);
             }
           }
         }
         if (!ok) continue;
-        if (j == n_tiles - 1) PROXY_FENCE();                     // the zeroed rows visible to the tensor core
+        if (j == n_tiles - 1 || rows_before > 0) PROXY_FENCE();   // the zeroed rows visible to the tensor core
         TC_FENCE_BEFORE();                                       // P is in tensor memory before the arrival
         mbar_arrive(&sh->p_full[gt & 1]);
         if (stored >= 0) {
@@ -718,7 +732,8 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 
 // 1 if this kernel takes the case (else the caller uses the mma.sync kernel).
 JV_EXPORT int jv_attn_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size, int window) {
-  if (head_dim != 128 || window != 0 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
+  (void)window;                 // every mask of common.cuh's first_visible is taken
+  if (head_dim != 128 || n_kv_heads < 1 || n_q_heads % n_kv_heads) return 0;
   const int G = n_q_heads / n_kv_heads;
   if (G > 16) return 0;
   return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
@@ -732,12 +747,13 @@ JV_EXPORT int jv_attn_tcgen05_tokens_per_tile(int n_q_heads, int n_kv_heads) { r
 // tiles of jv_attn_tcgen05_tokens_per_tile tokens, in ascending order of work.
 // sigmoid != 0: the weights are sigmoid(q.k * scale + bias[query head]) instead of a softmax (bias: [n_q_heads] floats or null).
 // head_scale [n_q_heads], dist_bias [n_q_heads][n_dist], sink [n_q_heads] (floats, each may be null; softmax only): see Params.
+// window: the mask as one number (0: every earlier key; > 0: a window; < 0: chunks of -window positions).
 JV_EXPORT int jv_attn_tcgen05_ex(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
                                  const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,
                                  const int* start_pos, const int* work, int n_work, int n_q_heads, int n_kv_heads,
                                  int head_dim, int page_size, int num_pages, float scale, int sigmoid, const float* bias,
                                  const float* head_scale, const float* dist_bias, int n_dist, const float* sink,
-                                 int* status, cudaStream_t stream) {
+                                 int window, int* status, cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
   if ((dist_bias != nullptr && n_dist < 1) || (sigmoid && (head_scale != nullptr || dist_bias != nullptr || sink != nullptr)))
     return JV_ERR_UNSUPPORTED;
@@ -776,7 +792,7 @@ JV_EXPORT int jv_attn_tcgen05_ex(const void* q, int q_stride, int n_tokens, void
   p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_work = n_work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
   p.scale_log2 = scale * LOG2E; p.status = status; p.sigmoid = sigmoid ? 1 : 0; p.bias = bias;
-  p.head_scale = head_scale; p.dist_bias = dist_bias; p.n_dist = n_dist; p.sink = sink;
+  p.head_scale = head_scale; p.dist_bias = dist_bias; p.n_dist = n_dist; p.sink = sink; p.window = window;
   constexpr size_t smem = TILE_BYTES * (Q_BUFFERS + K_STAGES + V_STAGES) + sizeof(Shared) + 1024;
   static bool ready[JV_MAX_DEVICES];
   if (!jv_once_per_device(ready, [&] {
@@ -801,5 +817,5 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
                               int head_dim, int page_size, int num_pages, float scale, int* status, cudaStream_t stream) {
   return jv_attn_tcgen05_ex(q, q_stride, n_tokens, out, out_stride, k_cache, v_cache, block_table, table_width, cu_seqlens,
                             start_pos, work, n_work, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, scale, 0, nullptr,
-                            nullptr, nullptr, 0, nullptr, status, stream);
+                            nullptr, nullptr, 0, nullptr, 0, status, stream);
 }

@@ -10,7 +10,7 @@
 // fresh slot is zero, which is the zero padding.  All arithmetic is 32-bit, whatever the types of in and out.
 //
 // A thread owns one channel of one segment of SEG tokens of one entry and slides a window of taps - 1 registers over
-// it.  Segments are counted per entry, so only an entry's first segment reads the state; the thread of that segment
+// it (SEG is at least taps - 1).  Segments are counted per entry, so only an entry's first segment reads the state; the thread of that segment
 // is also the ONE writer of the entry's state for its channel: it has the old state in its window before it writes
 // the new one (the entry's last taps - 1 inputs, or old state shifted where the entry is shorter), so no other
 // thread reads what it overwrites.  Blocks find their (entry, segment) from cu_seqlens; the grid is an upper bound,
@@ -18,8 +18,9 @@
 #include "common.cuh"
 
 namespace {
-constexpr int SEG = 64;
+constexpr int SEG = 32;
 constexpr int THREADS = 128;
+constexpr int BATCH = 8;       // inputs a thread asks for before it uses the first
 
 struct ConvParams {
   const void* in; long long in_stride;
@@ -83,17 +84,25 @@ __global__ void __launch_bounds__(THREADS) short_conv_kernel(const ConvParams p)
       st[(size_t)j * p.channels] = v;
     }
   }
-  for (int i = i0; i < i1; ++i) {
-    const float x = to_f32(in[(size_t)(t_begin + i) * p.in_stride]);
-    float acc = wt[K] * x;
+  // BATCH tokens at a time: their loads are under way together (a thread's tokens lie a whole row apart)
+  for (int i = i0; i < i1; i += BATCH) {
+    float xs[BATCH];
 #pragma unroll
-    for (int k = 0; k < K; ++k) acc = fmaf(wt[k], win[k], acc);
+    for (int u = 0; u < BATCH; ++u) xs[u] = i + u < i1 ? to_f32(in[(size_t)(t_begin + i + u) * p.in_stride]) : 0.f;
 #pragma unroll
-    for (int k = 0; k + 1 < K; ++k) win[k] = win[k + 1];
-    if (K > 0) win[K - 1] = x;
-    float y = p.residual ? x + acc : acc + b;
-    if (p.act == 1) y = y / (1.f + expf(-y));
-    out[(size_t)(t_begin + i) * p.out_stride] = from_f32<TO>(y);
+    for (int u = 0; u < BATCH; ++u) {
+      if (i + u >= i1) break;
+      const float x = xs[u];
+      float acc = wt[K] * x;
+#pragma unroll
+      for (int k = 0; k < K; ++k) acc = fmaf(wt[k], win[k], acc);
+#pragma unroll
+      for (int k = 0; k + 1 < K; ++k) win[k] = win[k + 1];
+      if (K > 0) win[K - 1] = x;
+      float y = p.residual ? x + acc : acc + b;
+      if (p.act == 1) y = y / (1.f + expf(-y));
+      out[(size_t)(t_begin + i + u) * p.out_stride] = from_f32<TO>(y);
+    }
   }
 }
 

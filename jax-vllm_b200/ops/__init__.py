@@ -736,8 +736,8 @@ def attn_tcgen05_supports(dtype: torch.dtype, head_dim: int, n_q_heads: int, n_k
                           window: int) -> bool:
     """Whether the tcgen05 prompt-attention kernel takes the case (csrc/attn_tcgen05.cu)."""
     g = n_q_heads // max(n_kv_heads, 1)
-    return (dtype == torch.bfloat16 and head_dim == 128 and not window and n_q_heads % n_kv_heads == 0
-            and 1 <= g <= 16 and page_size in (8, 16, 32, 64, 128))
+    return (dtype == torch.bfloat16 and head_dim == 128 and n_q_heads % n_kv_heads == 0
+            and 1 <= g <= 16 and page_size in (8, 16, 32, 64, 128))      # any mask (`window`) is taken
 
 
 def attn_tcgen05_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
@@ -748,11 +748,12 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
                  block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
                  n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, sigmoid: bool = False,
                  bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
-                 dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> None:
+                 dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None, window: int = 0) -> None:
     """Paged causal attention of prompt portions on tcgen05 tensor cores with scores and output in tensor
     memory (csrc/attn_tcgen05.cu); `work` lists 128-row tiles of `attn_tcgen05_tokens_per_tile` tokens.  With
     `sigmoid` the weight of a visible key is sigmoid(score * scale + bias[query head]) instead of a softmax;
-    `head_scale`, `dist_bias` and `sink` as for `attn_simt` (softmax only)."""
+    `head_scale`, `dist_bias` and `sink` as for `attn_simt` (softmax only); `window`: the mask as one number
+    (`mask_code`)."""
     n_dist = _score_extras("attn_tcgen05", n_q_heads, head_scale, dist_bias, sink)
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm not in ("q", "out")))     # q and out may be some heads of wider rows
@@ -769,11 +770,11 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
     f = _fn("attn_tcgen05", "jv_attn_tcgen05_ex", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                    c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                   c_void_p, c_void_p])
+                                                   c_int, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
              n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1], k_cache.shape[0], float(scale),
-             1 if sigmoid else 0, _ptr(bias), _ptr(head_scale), _ptr(dist_bias), n_dist, _ptr(sink),
+             1 if sigmoid else 0, _ptr(bias), _ptr(head_scale), _ptr(dist_bias), n_dist, _ptr(sink), int(window),
              _status_ptr(q.device), _stream()), "attn_tcgen05")
 
 

@@ -42,7 +42,7 @@ class Attention(Part):
         self.use_mma = ops.attn_mma_supports(ctx.dtype, self.d)
         if self.use_mma:
             self.kernels = ("rope_kv", "attn_mma", "gemm_simt", "linear_skinny")
-            if self.d == 128 and not self.window:
+            if self.d == 128:
                 self.kernels += ("attn_tcgen05", "attn_decode_tcgen05")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
@@ -88,7 +88,7 @@ class Attention(Part):
 
     def tile_classes(self, page_size: int):
         """Entries of several tokens: tiles of the mma.sync (or CUDA-core) kernel, and for portions that fill
-        a 128-row tile of the tcgen05 kernel (head size 128, bfloat16, no window) tiles of that one."""
+        a 128-row tile of the tcgen05 kernel (head size 128, bfloat16, any mask) tiles of that one."""
         small = (ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile)(self.hq, self.hkv)
         if ops.attn_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hkv, page_size, self.window):
             big = ops.attn_tcgen05_tokens_per_tile(self.hq, self.hkv)
@@ -139,7 +139,7 @@ class Attention(Part):
                 continue
             if cls[2] == self.FOREVER and cls[1] > 2:      # the class of whole 128-row tiles
                 ops.attn_tcgen05(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d,
-                                 self.spec.scale)
+                                 self.spec.scale, window=self.window)
             else:
                 kernel(qkv, qkv.stride(0), out, *common, work, n_work, self.hq, self.hkv, self.d, self.window,
                        self.spec.scale)

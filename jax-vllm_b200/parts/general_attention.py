@@ -113,7 +113,7 @@ class GeneralAttention(Part):
         # heads of 128 with sigmoid weights, or with a softmax that has a temperature per head, a bias by distance or a
         # sink: prompt portions that fill a 128-row tile go to the tcgen05 kernel
         self.big_tiles = (self.general is not None and not spec.score_cap and self.hv == self.hk and self.dv == self.d == 128
-                          and spec.twin is None and (spec.weights == "sigmoid") != bool(self.extras) and not self.mask)
+                          and spec.twin is None and (spec.weights == "sigmoid") != bool(self.extras))
         if self.big_tiles:
             self.kernels += ("attn_tcgen05",)
         self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
@@ -296,7 +296,7 @@ class GeneralAttention(Part):
             if n_work and cls[1] > 2:                      # the class of whole 128-row tiles
                 ops.attn_tcgen05(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, s.scale,
                                  sigmoid=s.weights == "sigmoid", bias=self.bias, head_scale=self.head_scale,
-                                 dist_bias=self.dist_bias, sink=self.sink)
+                                 dist_bias=self.dist_bias, sink=self.sink, window=self.mask)
             elif n_work:
                 kernel(work, n_work)
         dwork, n_dec = step.decode_work

@@ -62,7 +62,7 @@ class LatentAttention(Part):
             self.kernels = ("latent_prepare", "attn_latent_mma", "gemm_simt", "linear_skinny")
         if self.use_mma:
             self.kernels = ("latent_prepare", "attn_mma", "gemm_simt", "linear_skinny")
-            if self.dk == 128 and not self.mask:
+            if self.dk == 128:
                 self.kernels += ("attn_tcgen05", "attn_decode_tcgen05")
         if self.dq is not None:
             self.kernels += ("head_prepare",)
@@ -215,7 +215,7 @@ class LatentAttention(Part):
                 continue
             if big and cls[0] == big:                      # whole tiles of the tcgen05 kernel, one head group at a time
                 for qg, og in groups:
-                    ops.attn_tcgen05(qg, q.stride(0), og, *common, work, n_work, g, 1, dk, self.spec.scale)
+                    ops.attn_tcgen05(qg, q.stride(0), og, *common, work, n_work, g, 1, dk, self.spec.scale, window=self.mask)
             else:
                 kernel(q, q.stride(0), out, *common, work, n_work, H, 1, dk, self.mask, self.spec.scale, **extra)
         dwork, n_dec = step.decode_work

@@ -33,28 +33,40 @@ def oracle(c, w, tokens):
     return gp.forward(c, w, tokens).to(torch.float32)
 
 
-def compare(steps, out_dir, vocab, want, dtype, case=None, sensitive=0.0):
+def rounding_error(c, w, tokens):
+    """Per position, how far the plain logits move when the operands and the result of every matrix product are
+    rounded to bfloat16 and nothing else is: what rounding alone does to this model at this token."""
+    bf = lambda x: x.to(torch.bfloat16).to(torch.float64)
+    exact = gp.forward(c, w, tokens)
+    plain_matmul = torch.Tensor.__matmul__
+    torch.Tensor.__matmul__ = lambda a, b: bf(plain_matmul(bf(a), bf(b)))
+    try:
+        rounded = gp.forward(c, w, tokens)
+    finally:
+        torch.Tensor.__matmul__ = plain_matmul
+    return (rounded - exact).abs().max(dim=1).values
+
+
+def compare(steps, out_dir, vocab, want, dtype, case=None, rounding=None):
     """Every written row against the oracle's.  32-bit holds every position and the greedy token.  In bfloat16 one
-    position in fifty (or one) may be over the limit by up to half of it.  `sensitive`: the share of bfloat16
-    positions that may be over the limit by any amount, for models drawn at random whose narrow heads let two terms
-    cancel before a unit norm at some tokens (rounding of the terms then sets the result); the median difference
-    still has to lie under a third of the limit."""
+    position in fifty (or one) may be over the limit by up to half of it.  `rounding` (request -> `rounding_error`):
+    a bfloat16 position's limit is at least three times what rounding alone does there, for models drawn at random
+    whose narrow heads let two terms cancel before a unit norm at some tokens."""
     from tests.conftest import record_worst
     got = collect(steps, out_dir, vocab)
-    worst, lim_of_worst, total, slightly, far_off, ratios = 0.0, 0.0, 0, 0, 0, []
+    worst, lim_of_worst, total, slightly = 0.0, 0.0, 0, 0
     for rid, rows in got.items():
-        lim = limits(dtype, want[rid])
+        lim_all = limits(dtype, want[rid])
         for pos, row in rows.items():
             total += 1
+            lim = lim_all
+            if rounding is not None and dtype != "float32":
+                lim = max(lim, 3.0 * float(rounding[rid][pos]))
             w = want[rid][pos]
             diff = (torch.from_numpy(row.copy()) - w).abs().max().item()
             assert math.isfinite(diff), f"{rid} position {pos}: not a number"
-            ratios.append(diff / lim)
             if dtype != "float32" and lim < diff <= 1.5 * lim:
                 slightly += 1
-                continue
-            if dtype != "float32" and sensitive and diff > lim:
-                far_off += 1
                 continue
             assert diff <= lim, f"{rid} position {pos}: |diff| {diff:.3e} > {lim:.3e}"
             if diff >= worst:
@@ -62,11 +74,9 @@ def compare(steps, out_dir, vocab, want, dtype, case=None, sensitive=0.0):
             if dtype == "float32":
                 top2 = w.topk(2).values
                 assert int(row.argmax()) == int(w.argmax()) or float(top2[0] - top2[1]) < 1e-4
-    if sensitive and dtype != "float32":
-        assert slightly + far_off <= sensitive * total, f"{slightly + far_off} of {total} positions are over the limit"
-        assert sorted(ratios)[len(ratios) // 2] < 1 / 3, "the median difference is more than a third of the limit"
-    else:
-        assert slightly <= max(1, 0.02 * total), f"{slightly} of {total} positions are over the limit"
+    # the rounding of a run is one draw of what `rounding_error` estimates: with it, one position in ten may be over
+    share = 0.1 if rounding is not None else 0.02
+    assert slightly <= max(1, share * total), f"{slightly} of {total} positions are over the limit"
     if case is not None:
         record_worst(case, dtype, worst, lim_of_worst)
     return got
@@ -279,6 +289,57 @@ def test_windows_chunks_and_sinks_on_every_attention_kernel(name, mask):
             other = gp.softmax_attend(torch.cat([pad, qs[e].double()]), ks[e], vs[e], scale,
                                       torch.cat([gp.visible(c + q)[:c], wider]), sd)[c:]
             assert (other - want).abs().max() > 1e-3, f"entry {e}: the mask does not matter here"
+        at += q
+
+
+@pytest.mark.parametrize("mask", [("window", 1), ("window", 72), ("window", 200), ("chunk", 7), ("chunk", 120), ("chunk", 384),
+                                  ("chunk", 100000)])
+@pytest.mark.parametrize("Hq,Hk,sink_on", [(4, 2, False), (3, 3, True), (8, 1, True)])
+def test_windows_and_chunks_on_the_tcgen05_prompt_kernel(Hq, Hk, sink_on, mask):
+    """Whole 128-row tiles of a prompt portion on heads of 128 under a window or chunks: earlier context in the cache
+    whose pages before the first visible key have been given back (no page in the table), a last tile that is not
+    full, an entry that is exactly one tile from position 0; with and without a sink."""
+    from jax_vllm_b200 import ops
+    D, P, n_pages, scale = 128, 16, 64, 1.3 * 128 ** -0.5
+    tpt = ops.attn_tcgen05_tokens_per_tile(Hq, Hk)
+    ctx_new = [(300, 2 * tpt + 22), (0, tpt)]
+    window = mask[1] if mask[0] == "window" else None
+    chunk = mask[1] if mask[0] == "chunk" else None
+    code = ops.mask_code(window, chunk)
+    g = torch.Generator().manual_seed(Hq + mask[1])
+    table = scrambled_pages(ctx_new, P, n_pages, g)
+    kc = torch.full((n_pages, P, Hk, D), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full((n_pages, P, Hk, D), float("nan"), dtype=torch.bfloat16)
+    ks, vs, qs = [], [], []
+    for e, (c, q) in enumerate(ctx_new):
+        k = (torch.randn((c + q, Hk, D), generator=g) * 1.5).to(torch.bfloat16)
+        v = torch.randn((c + q, Hk, D), generator=g).to(torch.bfloat16)
+        first_needed = int(torch.nonzero(gp.visible(c + q, window=window, chunk=chunk)[c])[0])     # of the entry's first query
+        for j in range(c + q):
+            if (j // P + 1) * P <= first_needed:
+                table[e, j // P] = -1                       # the page went back to the pool
+            else:
+                kc[table[e, j // P], j % P], vc[table[e, j // P], j % P] = k[j], v[j]
+        ks.append(k.double().repeat_interleave(Hq // Hk, dim=1)); vs.append(v.double().repeat_interleave(Hq // Hk, dim=1))
+        qs.append((torch.randn((q, Hq, D), generator=g) * 1.5).to(torch.bfloat16))
+    sink = (torch.randn(Hq, generator=g) + 2.0) if sink_on else None
+    n = sum(q for _, q in ctx_new)
+    q_all = torch.cat(qs).reshape(n, Hq * D).cuda()
+    cu = torch.tensor([0, ctx_new[0][1], n], dtype=torch.int32).cuda()
+    start = torch.tensor([c for c, _ in ctx_new], dtype=torch.int32).cuda()
+    out = torch.full((n, Hq * D), float("nan"), dtype=torch.bfloat16).cuda()
+    tiles = [(e, t) for e, (_, q) in enumerate(ctx_new) for t in range(0, q, tpt)]
+    ops.attn_tcgen05(q_all, Hq * D, out, kc.cuda(), vc.cuda(), table.cuda(), cu, start,
+                     torch.tensor(tiles, dtype=torch.int32).cuda(), len(tiles), Hq, Hk, D, scale,
+                     sink=None if sink is None else sink.cuda(), window=code)
+    ops.check_status()
+    got = out.cpu().double().view(n, Hq, D)
+    at = 0
+    for e, (c, q) in enumerate(ctx_new):
+        pad = torch.zeros((c, Hq, D), dtype=torch.float64)
+        want = gp.softmax_attend(torch.cat([pad, qs[e].double()]), ks[e], vs[e], scale, gp.visible(c + q, window=window, chunk=chunk),
+                                 None if sink is None else sink.double())[c:]
+        assert (got[at:at + q] - want).abs().max() < 2.5e-2 * max(1.0, want.abs().max().item()), f"entry {e}"
         at += q
 
 
@@ -579,6 +640,7 @@ def test_configurations_drawn_at_random(seed, tmp_path):
     page = [4, 8, 16, 32][seed % 4]
     seqs = {f"r{i}": random_tokens(n, c["vocab"], seed=200 + 10 * seed + i) for i, n in enumerate([90, 33, 61, 12, 40])}
     want = {rid: oracle(c, w, t) for rid, t in seqs.items()}
+    rounding = {rid: rounding_error(c, w, seqs[rid]) for rid in ("r0", "r2")}
     from jax_vllm_b200.engine.replay import Replayer
     for dtype in ("float32", "bfloat16"):
         for k, steps in enumerate((whole("r0", seqs["r0"]), portions("r0", seqs["r0"], (3, 1, 30, 2)),
@@ -586,7 +648,7 @@ def test_configurations_drawn_at_random(seed, tmp_path):
             out = tmp_path / f"{dtype}_{k}"
             rep = Replayer(folder, dtype, out, max_tokens=128, page_size=page)
             rep.run_stream(json.dumps(s) for s in steps)
-            compare(steps, out, c["vocab"], want, dtype, sensitive=0.1)
+            compare(steps, out, c["vocab"], want, dtype, rounding=rounding)
     steps = mixed_trace(seqs)
     rep = Replayer(folder, "float32", tmp_path / "mixed", max_tokens=320, page_size=page)
     rep.run_stream(json.dumps(s) for s in steps)
