@@ -21,7 +21,7 @@ class NormSpec:
     eps: float
     name: str                      # tensor name of the weight, relative to the owner's prefix
     kind: str = "rmsnorm"          # "rmsnorm", or "dyt": tanh(alpha * x) * weight + bias (`<name>.alpha`, `<name>.b`)
-    offset: float = 0.0            # rmsnorm: the stored weight plus this number multiplies (1.0: a weight stored around zero)
+    offset: float = 0.0            # rmsnorm: the stored weight plus this number multiplies (1.0: the file holds weight - 1)
 
 
 @dataclass(frozen=True)

@@ -89,8 +89,9 @@ class GeneralAttention(Part):
             if self.position is None or self.dv % 2:
                 raise ValueError("rotated values need a position encoding and an even value size")
             self.value_freq = self.position.frequencies(self.dv).to(ctx.device)
-        if self.by_head:
-            self.kernels = self.kernels + ("head_prepare",)
+        if self.by_head:            # neither the whole-projection preparation nor (without a gate) the finishing kernel runs
+            unused = ("attn_prepare",) + (("attn_finish",) if spec.gate is None else ())
+            self.kernels = tuple(k for k in self.kernels if k not in unused) + ("head_prepare",)
         # Which attention kernel: once queries and keys are prepared, a mixer with one softmax map, no cap and
         # values shaped like its keys IS the plain grouped-query attention, and goes the way of that mixer (the
         # tcgen05 kernels for heads of 128, mma.sync for 16/32/64, in bfloat16).  Every other bfloat16 mixer with

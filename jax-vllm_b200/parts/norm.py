@@ -1,6 +1,6 @@
 """RMSNorm over the hidden axis: y = h * rsqrt(mean(h^2) + eps) * weight, in 32-bit
 (jllm/model/common.py:44-48), fused with the residual sum before it.  With an `offset` the
-stored weight is kept around zero and weight + offset multiplies (formed once, in 32-bit,
+file holds weight - offset, and stored + offset multiplies (formed once, in 32-bit,
 when the weights are bound)."""
 
 from __future__ import annotations

@@ -107,7 +107,7 @@ def tensor_shapes(c: dict) -> dict:
 
 def make_weights(c: dict, seed: int, up_scale: float = 1.5) -> dict:
     """Random float32 weights: matrices N(0, 1.5/sqrt(fan_in)) (the feed-forwards' first matrices `up_scale` instead
-    of 1.5: their results are squared), the embedding of order one, norm weights stored around zero N(0, 0.1) (the
+    of 1.5: their results are squared), the embedding of order one, the layers' norm weights N(0, 0.1) (one is added to them) (the
     query, key, latent and state-space norms around one), convolutions N(0, 0.5), sinks N(0, 1), A_log around -1, step
     biases around 0, skips around 1."""
     g = torch.Generator().manual_seed(seed)

@@ -60,7 +60,7 @@ def unit(y: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def offset_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """The layers' norm: the weight is stored around zero."""
+    """The layers' norm: one is added to the stored weight."""
     return unit(x, eps) * (1.0 + w)
 
 
