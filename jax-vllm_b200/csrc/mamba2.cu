@@ -43,30 +43,50 @@ __global__ void __launch_bounds__(32 * WARPS) mamba_prepare_kernel(const T* __re
   }
 }
 
+// A thread keeps up to KEEP of its group's gated values in registers between the sum of squares and the write (a
+// group of up to KEEP * blockDim elements is then read once); a longer group is formed twice.
+constexpr int KEEP = 8;
+
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128) mamba_finish_kernel(const float* __restrict__ o, const T* __restrict__ x,
-                                                           long long x_stride, const T* __restrict__ z, long long z_stride,
-                                                           const TW* __restrict__ skip, const TW* __restrict__ w,
-                                                           T* __restrict__ out, long long out_stride, float eps, int value_dim,
-                                                           int group_size, int inner) {
+__global__ void __launch_bounds__(1024) mamba_finish_kernel(const float* __restrict__ o, const T* __restrict__ x,
+                                                            long long x_stride, const T* __restrict__ z, long long z_stride,
+                                                            const TW* __restrict__ skip, const TW* __restrict__ w,
+                                                            T* __restrict__ out, long long out_stride, float eps, int value_dim,
+                                                            int group_size, int inner) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, first = blockIdx.y * group_size;
-  const float* ot = o + (size_t)t * inner;
-  const T* xt = x + (size_t)t * x_stride;
-  const T* zt = z + (size_t)t * z_stride;
-  float ss = 0.f;
-  for (int i = first + threadIdx.x; i < first + group_size; i += blockDim.x) {
+  const float* ot = o + (size_t)t * inner + first;
+  const T* xt = x + (size_t)t * x_stride + first;
+  const T* zt = z + (size_t)t * z_stride + first;
+  auto gated = [&](int i) {
     const float zz = to_f32(zt[i]);
-    const float y = (ot[i] + to_f32(skip[i / value_dim]) * to_f32(xt[i])) * (zz / (1.f + expf(-zz)));
-    ss += y * y;
+    return (ot[i] + to_f32(skip[(first + i) / value_dim]) * to_f32(xt[i])) * (zz / (1.f + expf(-zz)));
+  };
+  const bool kept = group_size <= KEEP * (int)blockDim.x;
+  float ys[KEEP];
+  float ss = 0.f;
+  if (kept) {
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      ys[u] = i < group_size ? gated(i) : 0.f;
+      ss += ys[u] * ys[u];
+    }
+  } else {
+    for (int i = threadIdx.x; i < group_size; i += blockDim.x) { const float y = gated(i); ss += y * y; }
   }
   const float inv = rsqrtf(block_sum(ss, scratch) / (float)group_size + eps);
-  for (int i = first + threadIdx.x; i < first + group_size; i += blockDim.x) {
-    const float zz = to_f32(zt[i]);
-    const float y = (ot[i] + to_f32(skip[i / value_dim]) * to_f32(xt[i])) * (zz / (1.f + expf(-zz)));
-    out[(size_t)t * out_stride + i] = from_f32<T>(y * inv * to_f32(w[i]));
+  T* dst = out + (size_t)t * out_stride + first;
+  if (kept) {
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      if (i < group_size) dst[i] = from_f32<T>(ys[u] * inv * to_f32(w[first + i]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < group_size; i += blockDim.x) dst[i] = from_f32<T>(gated(i) * inv * to_f32(w[first + i]));
   }
 }
 }  // namespace
@@ -95,8 +115,11 @@ JV_EXPORT int jv_mamba_finish(const float* o, const void* x, long long x_stride,
   if (n == 0) return JV_OK;
   const int inner = heads * value_dim;
   if (heads < 1 || value_dim < 1 || norm_groups < 1 || inner % norm_groups) return JV_ERR_UNSUPPORTED;
+  // two elements a thread where the group allows: many warps hide the loads' latency when there are few tokens
+  int threads = ((inner / norm_groups + 1) / 2 + 31) / 32 * 32;
+  threads = threads < 32 ? 32 : threads > 1024 ? 1024 : threads;
   JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,
-      return jv_launch(mamba_finish_kernel<T, TW>, dim3(n, norm_groups), dim3(128), 0, stream, o, (const T*)x, x_stride,
+      return jv_launch(mamba_finish_kernel<T, TW>, dim3(n, norm_groups), dim3(threads), 0, stream, o, (const T*)x, x_stride,
                        (const T*)z, z_stride, (const TW*)skip, (const TW*)w, (T*)out, out_stride, eps, value_dim,
                        inner / norm_groups, inner)));
   return JV_ERR_UNSUPPORTED;
